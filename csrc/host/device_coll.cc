@@ -1,0 +1,558 @@
+// device_coll.cc -- host side of the device path: turns one collective call into
+// one (or, for unregistered buffers larger than the staging area, a few) kernel
+// launches: finds out whether the buffers are peer-visible, asks the tuner for an
+// algorithm and CTA count, fills the argument block and launches.
+//
+// Buffers inside a registered window are used in place by every rank (offsets are
+// symmetric, as with NCCL window registration).  Anything else is staged through
+// the communicator's internal window inside the same kernel.
+#include <algorithm>
+
+#include "../kernels/launch.h"
+#include "comm.h"
+#include "tuner.h"
+
+namespace fcx {
+
+namespace {
+
+enum Family { kFamReduce = 0, kFamCopy = 1, kFamNvls = 2 };
+
+struct BufView {
+  Window *win = nullptr;
+  size_t off = 0;
+  bool visible() const { return win != nullptr; }
+};
+
+BufView viewOf(flagcxComm *c, const void *p, size_t bytes) {
+  BufView v;
+  if (c->emu || !p) return v;
+  v.win = c->windows.find(p, bytes ? bytes : 1);
+  if (v.win) v.off = (uintptr_t)p - (uintptr_t)v.win->local;
+  return v;
+}
+
+// In an emulated world every buffer is visible to every rank; the launcher fills
+// the other ranks' entries when all of them have posted.
+bool emuVisible(flagcxComm *c) { return c->emu && !getEnv("FLAGCX_EMU_FORCE_STAGING"); }
+
+void setIn(flagcxComm *c, CollArgs &a, const BufView &v, const void *local, size_t extraOff = 0) {
+  for (int p = 0; p < c->nranks; ++p) a.in[p] = nullptr;
+  if (v.win) {
+    for (int p = 0; p < c->nranks; ++p) a.in[p] = (const char *)v.win->peer[p] + v.off + extraOff;
+    if (v.win->mc) a.mcIn = (const char *)v.win->mc + v.off + extraOff;
+  } else {
+    a.in[c->rank] = (const char *)local + extraOff;
+  }
+}
+void setOut(flagcxComm *c, CollArgs &a, const BufView &v, void *local, size_t extraOff = 0) {
+  for (int p = 0; p < c->nranks; ++p) a.out[p] = nullptr;
+  if (v.win) {
+    for (int p = 0; p < c->nranks; ++p) a.out[p] = (char *)v.win->peer[p] + v.off + extraOff;
+    if (v.win->mc) a.mcOut = (char *)v.win->mc + v.off + extraOff;
+  } else {
+    a.out[c->rank] = (char *)local + extraOff;
+  }
+}
+// Staging region [off, off+...) of every rank.
+void setInStage(flagcxComm *c, CollArgs &a, size_t off) {
+  BufView v{c->internalWin, c->layout.stagingOff + off};
+  setIn(c, a, v, nullptr);
+}
+void setOutStage(flagcxComm *c, CollArgs &a, size_t off) {
+  BufView v{c->internalWin, c->layout.stagingOff + off};
+  setOut(c, a, v, nullptr);
+}
+
+void initArgs(flagcxComm *c, CollArgs &a, int kind, flagcxDataType_t dt) {
+  memset(&a, 0, sizeof a);
+  a.kind = kind;
+  a.dtype = dt;
+  a.elemSize = (int)getFlagcxDataTypeSize(dt);
+  a.scale = 1.0f;
+  a.flags = kFlagBeginBarrier | kFlagEndBarrier;
+  for (int p = 0; p < c->nranks; ++p)
+    a.meta[p] = (unsigned long long *)((char *)c->internalWin->peer[p] + c->layout.metaOff);
+}
+
+flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, cudaStream_t stream) {
+  nCtas = std::max(1, std::min(nCtas, FLAGCX_COLL_BARRIER_SLOTS));
+  if (c->emu) return emuSubmit(c, family, &a, nullptr, nCtas, stream);
+  LaunchCtx lc;
+  lc.comm = &c->dev;
+  lc.stream = stream;
+  lc.nCtas = nCtas;
+  cudaError_t e = family == kFamReduce ? launchReduceKernel(lc, a, c->nranks)
+                  : family == kFamCopy ? launchCopyKernel(lc, a)
+                                       : launchNvlsKernel(lc, a);
+  if (e != cudaSuccess) {
+    FCX_WARN("kernel launch failed: %s", cudaGetErrorString(e));
+    return flagcxUnhandledDeviceError;
+  }
+  return flagcxSuccess;
+}
+
+bool isFloatType(flagcxDataType_t t) {
+  return t == flagcxFloat16 || t == flagcxFloat32 || t == flagcxFloat64 || t == flagcxBfloat16;
+}
+
+// Reduction operator and epilogue fields common to the reduce family.
+flagcxResult_t setReduceEpilogue(flagcxComm *c, CollArgs &a, const DeviceCollRequest &rq) {
+  a.redOp = rq.redOp == flagcxAvg ? kOpSum : (int)rq.redOp;
+  a.scale = rq.scale;
+  a.divisor = 0;
+  if (rq.redOp == flagcxAvg) {
+    if (isFloatType(rq.dtype)) a.scale *= 1.0f / (float)c->nranks;
+    else a.divisor = c->nranks;
+  }
+  a.outMode = kOutSame;
+  if (rq.outDtype != flagcxNumTypes && rq.outDtype != rq.dtype) {
+    if (rq.outDtype == flagcxFloat32 && (rq.dtype == flagcxBfloat16 || rq.dtype == flagcxFloat16)) a.outMode = kOutFloat;
+    else if (rq.outDtype == flagcxBfloat16 && rq.dtype == flagcxFloat32) a.outMode = kOutBf16;
+    else {
+      FCX_WARN("fused cast %s -> %s is not supported", dtypeName(rq.dtype), dtypeName(rq.outDtype));
+      return flagcxInvalidArgument;
+    }
+  }
+  a.residual = (const char *)rq.residual;
+  return flagcxSuccess;
+}
+
+size_t outElemSize(const CollArgs &a) {
+  return a.outMode == kOutFloat ? 4 : a.outMode == kOutBf16 ? 2 : (size_t)a.elemSize;
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+bool nvlsEligible(flagcxComm *c, const DeviceCollRequest &rq, size_t count) {
+  if (!c->nvls || c->emu) return false;
+  if (rq.dtype != flagcxFloat32 && rq.dtype != flagcxBfloat16 && rq.dtype != flagcxFloat16) return false;
+  bool addLike = rq.redOp == flagcxSum || rq.redOp == flagcxAvg;
+  bool minmax = (rq.redOp == flagcxMin || rq.redOp == flagcxMax) && rq.dtype != flagcxFloat32;
+  if (!addLike && !minmax) return false;
+  if (rq.residual || (rq.outDtype != flagcxNumTypes && rq.outDtype != rq.dtype)) return false;
+  size_t es = getFlagcxDataTypeSize(rq.dtype);
+  return (count * es) % 16 == 0 && aligned16(rq.send) && aligned16(rq.recv);
+}
+
+void note(flagcxComm *c, flagcxCommOp_t op, size_t bytes, int algo, int nCtas) {
+  OpStats &s = c->stats[op];
+  s.calls++;
+  s.bytes += bytes;
+  s.lastAlgo = algo;
+  s.lastCtas = nCtas;
+}
+
+int pickCtas(flagcxComm *c, const DeviceCollRequest &rq, const TuneChoice &ch) {
+  int n = rq.nCtas > 0 ? rq.nCtas : ch.nCtas;
+  return std::max(1, std::min(n, FLAGCX_COLL_BARRIER_SLOTS));
+}
+
+// ---------------------------------------------------------------------------
+flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  const int n = c->nranks;
+  CollArgs a;
+  initArgs(c, a, kAllReduceOneShot, rq.dtype);
+  FCXCHECK(setReduceEpilogue(c, a, rq));
+  const size_t es = a.elemSize, oes = outElemSize(a);
+  const size_t count = rq.count;
+  BufView vin = viewOf(c, rq.send, count * es), vout = viewOf(c, rq.recv, count * oes);
+  const bool inVis = vin.visible() || emuVisible(c), outVis = vout.visible() || emuVisible(c);
+  const bool nvlsOk = nvlsEligible(c, rq, count);
+  TuneChoice ch = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, inVis && outVis, nvlsOk);
+  int algo = rq.algo >= 0 ? rq.algo : ch.algo;
+  if ((algo == FLAGCX_ALGO_NVLS_ONESHOT || algo == FLAGCX_ALGO_NVLS_TWOSHOT) && !nvlsOk) algo = FLAGCX_ALGO_TWOSHOT;
+  if (algo != FLAGCX_ALGO_ONESHOT && algo != FLAGCX_ALGO_TWOSHOT && algo != FLAGCX_ALGO_NVLS_ONESHOT &&
+      algo != FLAGCX_ALGO_NVLS_TWOSHOT)
+    algo = FLAGCX_ALGO_TWOSHOT;
+  // one-shot writes its output while peers may still read the same addresses
+  if (algo == FLAGCX_ALGO_ONESHOT && rq.send == rq.recv && inVis) algo = FLAGCX_ALGO_TWOSHOT;
+  if (n == 1) algo = FLAGCX_ALGO_ONESHOT;
+  const int nCtas = pickCtas(c, rq, ch);
+  note(c, flagcxCommOpAllReduce, count * es, algo, nCtas);
+  const size_t S = c->layout.stagingBytes, half = S / 2;
+  const bool nvlsAlgo = algo == FLAGCX_ALGO_NVLS_ONESHOT || algo == FLAGCX_ALGO_NVLS_TWOSHOT;
+  // multimem needs multicast aliases: windows bound at registration, else the staging
+  const bool inMc = vin.win && vin.win->mc, outMc = vout.win && vout.win->mc;
+
+  if (algo == FLAGCX_ALGO_ONESHOT || algo == FLAGCX_ALGO_NVLS_ONESHOT) {
+    a.kind = nvlsAlgo ? kAllReduceNvlsOneShot : kAllReduceOneShot;
+    const bool direct = nvlsAlgo ? inMc : inVis;
+    if (direct) {
+      a.count = count;
+      setIn(c, a, vin, rq.send);
+      setOut(c, a, BufView(), rq.recv);
+      return launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream);
+    }
+    // staged input, alternating halves: the barrier of the next call proves that
+    // every peer finished reading this half, so no trailing barrier is needed
+    size_t chunk = half / es / 16 * 16;
+    for (size_t off = 0; off < count || off == 0; off += chunk) {
+      size_t cnt = std::min(chunk, count - off);
+      a.count = cnt;
+      setInStage(c, a, (c->stageParity & 1) * half);
+      c->stageParity++;
+      a.userIn = (const char *)rq.send + off * es;
+      a.nInBlocks = 1;
+      a.inBlockBytes = cnt * es;
+      setOut(c, a, BufView(), rq.recv, off * oes);
+      a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
+      a.flags = kFlagBeginBarrier;
+      FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
+      if (count == 0) break;
+    }
+    return flagcxSuccess;
+  }
+
+  // two-shot
+  a.kind = nvlsAlgo ? kAllReduceNvlsTwoShot : kAllReduceTwoShot;
+  const bool inDirect = nvlsAlgo ? inMc : inVis, outDirect = nvlsAlgo ? outMc : outVis;
+  if (inDirect && outDirect) {
+    a.count = count;
+    setIn(c, a, vin, rq.send);
+    setOut(c, a, vout, rq.recv);
+    return launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream);
+  }
+  size_t chunk = half / std::max(es, oes) / (16 * (size_t)n) * (16 * (size_t)n);
+  for (size_t off = 0; off < count || off == 0; off += chunk) {
+    size_t cnt = std::min(chunk, count - off);
+    a.count = cnt;
+    size_t slice = sliceElems(cnt, n, es);
+    if (inDirect) {
+      setIn(c, a, vin, rq.send, off * es);
+      a.userIn = nullptr;
+    } else {
+      setInStage(c, a, 0);
+      a.userIn = (const char *)rq.send + off * es;
+      a.nInBlocks = n;
+      a.inBlockBytes = slice * es;
+      a.userInStride = slice * es;
+      a.inTotalBytes = cnt * es;
+    }
+    if (outDirect) {
+      setOut(c, a, vout, rq.recv, off * oes);
+      a.userOut = nullptr;
+    } else {
+      setOutStage(c, a, half);
+      a.userOut = (char *)rq.recv + off * oes;
+      a.nOutBlocks = n;
+      a.outBlockBytes = slice * oes;
+      a.userOutStride = slice * oes;
+      a.outTotalBytes = cnt * oes;
+    }
+    a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
+    FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
+    if (count == 0) break;
+  }
+  return flagcxSuccess;
+}
+
+flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  const int n = c->nranks;
+  CollArgs a;
+  initArgs(c, a, kReduceScatter, rq.dtype);
+  FCXCHECK(setReduceEpilogue(c, a, rq));
+  const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
+  BufView vin = viewOf(c, rq.send, count * es * n);
+  const bool inVis = vin.visible() || emuVisible(c);
+  const bool nvlsOk = nvlsEligible(c, rq, count) && vin.win && vin.win->mc;
+  TuneChoice ch = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, inVis, nvlsOk);
+  int algo = rq.algo >= 0 ? rq.algo : ch.algo;
+  if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PULL;
+  const int nCtas = pickCtas(c, rq, ch);
+  note(c, flagcxCommOpReduceScatter, count * es * n, algo, nCtas);
+  if (inVis) {
+    a.kind = algo == FLAGCX_ALGO_NVLS ? kReduceScatterNvls : kReduceScatter;
+    a.count = count;
+    a.inStride = count * es;
+    setIn(c, a, vin, rq.send);
+    setOut(c, a, BufView(), rq.recv);
+    return launch(c, algo == FLAGCX_ALGO_NVLS ? kFamNvls : kFamReduce, a, nCtas, stream);
+  }
+  const size_t S = c->layout.stagingBytes;
+  size_t chunk = S / n / es / 16 * 16;
+  for (size_t off = 0; off < count || off == 0; off += chunk) {
+    size_t cnt = std::min(chunk, count - off);
+    a.count = cnt;
+    a.inStride = cnt * es;
+    setInStage(c, a, 0);
+    a.userIn = (const char *)rq.send + off * es;
+    a.nInBlocks = n;
+    a.inBlockBytes = cnt * es;
+    a.userInStride = count * es;
+    setOut(c, a, BufView(), rq.recv, off * oes);
+    a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
+    FCXCHECK(launch(c, kFamReduce, a, nCtas, stream));
+    if (count == 0) break;
+  }
+  return flagcxSuccess;
+}
+
+flagcxResult_t reduceToRoot(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  const int n = c->nranks;
+  CollArgs a;
+  initArgs(c, a, kReduceToRoot, rq.dtype);
+  FCXCHECK(setReduceEpilogue(c, a, rq));
+  a.root = rq.root;
+  const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
+  BufView vin = viewOf(c, rq.send, count * es);
+  const bool inVis = vin.visible() || emuVisible(c);
+  TuneChoice ch = c->tuner->choose(flagcxCommOpReduce, count * es, n, inVis, false);
+  const int nCtas = pickCtas(c, rq, ch);
+  note(c, flagcxCommOpReduce, count * es, FLAGCX_ALGO_PULL, nCtas);
+  if (inVis) {
+    a.count = count;
+    setIn(c, a, vin, rq.send);
+    setOut(c, a, BufView(), rq.recv);
+    return launch(c, kFamReduce, a, nCtas, stream);
+  }
+  const size_t S = c->layout.stagingBytes;
+  size_t chunk = S / es / 16 * 16;
+  for (size_t off = 0; off < count || off == 0; off += chunk) {
+    size_t cnt = std::min(chunk, count - off);
+    a.count = cnt;
+    setInStage(c, a, 0);
+    a.userIn = (const char *)rq.send + off * es;
+    a.nInBlocks = 1;
+    a.inBlockBytes = cnt * es;
+    setOut(c, a, BufView(), rq.recv, off * oes);
+    FCXCHECK(launch(c, kFamReduce, a, nCtas, stream));
+    if (count == 0) break;
+  }
+  return flagcxSuccess;
+}
+
+// ---- copy family: everything in bytes -----------------------------------------------
+struct CopyPlan {
+  flagcxCommOp_t op;
+  int pushKind, pullKind; // -1: not available
+  bool stagedBlocksPerRank; // staging holds n blocks (scatter, alltoall) instead of one
+};
+
+flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  const int n = c->nranks, me = c->rank;
+  const size_t es = getFlagcxDataTypeSize(rq.dtype);
+  const size_t blk = rq.count * es; // bytes per rank-block (or the whole message)
+  CollArgs a;
+  initArgs(c, a, kBarrierOnly, flagcxUint8);
+  a.elemSize = 1;
+  a.root = rq.root;
+
+  size_t sendBytes = blk, recvBytes = blk;
+  int pushKind = -1, pullKind = -1;
+  bool nBlocksIn = false; // the input holds one block per rank
+  switch (rq.op) {
+    case flagcxCommOpAllGather: recvBytes = blk * n; pushKind = kAllGatherPush; pullKind = kAllGatherPull; break;
+    case flagcxCommOpBroadcast: pushKind = kBroadcastPush; pullKind = kBroadcastPull; break;
+    case flagcxCommOpGather: recvBytes = blk * n; pullKind = kGatherPull; break;
+    case flagcxCommOpScatter: sendBytes = blk * n; pullKind = kScatterPull; nBlocksIn = true; break;
+    case flagcxCommOpAlltoAll:
+      sendBytes = recvBytes = blk * n; pushKind = kAllToAllPush; pullKind = kAllToAllPull; nBlocksIn = true;
+      break;
+    default: return flagcxInternalError;
+  }
+  // Rooted operations: only the root's send (scatter, broadcast) or recv (gather)
+  // argument is meaningful, so visibility is judged on the argument every rank has.
+  const bool sendEverywhere = rq.op != flagcxCommOpBroadcast && rq.op != flagcxCommOpScatter;
+  const bool recvEverywhere = rq.op != flagcxCommOpGather;
+  BufView vin = sendEverywhere ? viewOf(c, rq.send, sendBytes) : BufView();
+  BufView vout = recvEverywhere ? viewOf(c, rq.recv, recvBytes) : BufView();
+  const bool inVis = vin.visible() || (emuVisible(c) && sendEverywhere);
+  const bool outVis = vout.visible() || (emuVisible(c) && recvEverywhere);
+  const bool nvlsOk = rq.op == flagcxCommOpAllGather && c->nvls && !c->emu && vout.win && vout.win->mc &&
+                      blk % 16 == 0 && aligned16(rq.send);
+  TuneChoice ch = c->tuner->choose(rq.op, std::max(sendBytes, recvBytes), n, inVis || outVis, nvlsOk);
+  int algo = rq.algo >= 0 ? rq.algo : ch.algo;
+  if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PUSH;
+  if (algo == FLAGCX_ALGO_PUSH && !(outVis && pushKind >= 0)) algo = FLAGCX_ALGO_PULL;
+  if (algo == FLAGCX_ALGO_PULL && !inVis && outVis && pushKind >= 0) algo = FLAGCX_ALGO_PUSH; // avoids staging
+  if (algo != FLAGCX_ALGO_PUSH && algo != FLAGCX_ALGO_NVLS) algo = FLAGCX_ALGO_PULL;
+  const int nCtas = pickCtas(c, rq, ch);
+  note(c, rq.op, std::max(sendBytes, recvBytes), algo, nCtas);
+
+  if (algo == FLAGCX_ALGO_NVLS) {
+    a.kind = kAllGatherNvls;
+    a.dtype = flagcxFloat32; // multimem.st moves raw 16-byte packs
+    a.elemSize = 4;
+    a.count = blk / 4;
+    a.outStride = blk;
+    setIn(c, a, BufView(), rq.send);
+    setOut(c, a, vout, rq.recv);
+    return launch(c, kFamNvls, a, nCtas, stream);
+  }
+  if (algo == FLAGCX_ALGO_PUSH) {
+    a.kind = pushKind;
+    a.count = blk;
+    a.inStride = blk;
+    a.outStride = blk;
+    setIn(c, a, BufView(), rq.send);
+    setOut(c, a, vout, rq.recv);
+    return launch(c, kFamCopy, a, nCtas, stream);
+  }
+  a.kind = pullKind;
+  if (inVis) {
+    a.count = blk;
+    a.inStride = blk;
+    a.outStride = blk;
+    setIn(c, a, vin, rq.send);
+    setOut(c, a, BufView(), rq.recv);
+    return launch(c, kFamCopy, a, nCtas, stream);
+  }
+  // staged input
+  const size_t S = c->layout.stagingBytes;
+  size_t chunk = (nBlocksIn ? S / n : S) / 16 * 16;
+  const bool iStage = !(rq.op == flagcxCommOpBroadcast || rq.op == flagcxCommOpScatter) || me == rq.root;
+  for (size_t off = 0; off < blk || off == 0; off += chunk) {
+    size_t len = std::min(chunk, blk - off);
+    a.count = len;
+    a.inStride = len;   // staged blocks are packed
+    a.outStride = blk;  // the user's output keeps its own block stride
+    setInStage(c, a, 0);
+    a.userIn = iStage ? (const char *)rq.send + off : nullptr;
+    a.nInBlocks = nBlocksIn ? n : 1;
+    a.inBlockBytes = len;
+    a.userInStride = blk;
+    setOut(c, a, BufView(), rq.recv, off);
+    FCXCHECK(launch(c, kFamCopy, a, nCtas, stream));
+    if (blk == 0) break;
+  }
+  return flagcxSuccess;
+}
+
+flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  const int n = c->nranks, me = c->rank;
+  const size_t es = getFlagcxDataTypeSize(rq.dtype);
+  size_t sendSpan = 0, recvSpan = 0, total = 0;
+  for (int p = 0; p < n; ++p) {
+    sendSpan = std::max(sendSpan, (rq.sendDispls[p] + rq.sendCounts[p]) * es);
+    recvSpan = std::max(recvSpan, (rq.recvDispls[p] + rq.recvCounts[p]) * es);
+    total += rq.sendCounts[p] * es;
+  }
+  BufView vin = viewOf(c, rq.send, sendSpan);
+  const bool inVis = vin.visible() || emuVisible(c);
+  if (inVis) {
+    CollArgs a;
+    initArgs(c, a, kAllToAllvPull, rq.dtype);
+    for (int p = 0; p < n; ++p) {
+      a.sendCounts[p] = rq.sendCounts[p];
+      a.sendDispls[p] = rq.sendDispls[p];
+      a.recvCounts[p] = rq.recvCounts[p];
+      a.recvDispls[p] = rq.recvDispls[p];
+    }
+    setIn(c, a, vin, rq.send);
+    setOut(c, a, BufView(), rq.recv);
+    TuneChoice ch = c->tuner->choose(flagcxCommOpAlltoAllv, total, n, true, false);
+    const int nCtas = pickCtas(c, rq, ch);
+    note(c, flagcxCommOpAlltoAllv, total, FLAGCX_ALGO_PULL, nCtas);
+    return launch(c, kFamCopy, a, nCtas, stream);
+  }
+  // unregistered: n sends and n receives through the point-to-point slots
+  note(c, flagcxCommOpAlltoAllv, total, FLAGCX_ALGO_PULL, FLAGCX_P2P_CTAS);
+  for (int p = 0; p < n; ++p) {
+    c->groupOps.push_back({true, p, (char *)const_cast<void *>(rq.send) + rq.sendDispls[p] * es,
+                           rq.sendCounts[p] * es, stream});
+    c->groupOps.push_back({false, p, (char *)rq.recv + rq.recvDispls[p] * es, rq.recvCounts[p] * es, stream});
+  }
+  (void)me;
+  return deviceGroupLaunch(c);
+}
+
+} // namespace
+
+flagcxResult_t deviceBarrier(flagcxComm *c, cudaStream_t stream) {
+  CollArgs a;
+  initArgs(c, a, kBarrierOnly, flagcxUint8);
+  a.flags = kFlagBeginBarrier;
+  return launch(c, kFamCopy, a, 1, stream);
+}
+
+flagcxResult_t deviceCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
+  if (c->asyncError.load() != flagcxSuccess) {
+    FCX_WARN("communicator is in an error state; destroy it and create a new one");
+    return (flagcxResult_t)c->asyncError.load();
+  }
+  if (getFlagcxDataTypeSize(rq.dtype) == 0) return flagcxInvalidArgument;
+  switch (rq.op) {
+    case flagcxCommOpAllReduce: return allReduce(c, rq, stream);
+    case flagcxCommOpReduceScatter: return reduceScatter(c, rq, stream);
+    case flagcxCommOpReduce: return reduceToRoot(c, rq, stream);
+    case flagcxCommOpAllGather:
+    case flagcxCommOpBroadcast:
+    case flagcxCommOpGather:
+    case flagcxCommOpScatter:
+    case flagcxCommOpAlltoAll: return copyCollective(c, rq, stream);
+    case flagcxCommOpAlltoAllv: return allToAllv(c, rq, stream);
+    default: return flagcxInvalidArgument;
+  }
+}
+
+// Launches everything queued by flagcxSend/flagcxRecv since flagcxGroupStart.  Each
+// launch carries at most one message per peer and direction; later messages to the
+// same peer go into the next launch, in call order on both sides.
+flagcxResult_t deviceGroupLaunch(flagcxComm *c) {
+  std::vector<GroupOp> ops;
+  ops.swap(c->groupOps);
+  const int n = c->nranks;
+  size_t next = 0;
+  std::vector<char> used(ops.size(), 0);
+  size_t remaining = ops.size();
+  bool first = true;
+  while (remaining > 0 || (first && c->emu)) {
+    first = false;
+    P2pArgs a;
+    memset(&a, 0, sizeof a);
+    cudaStream_t stream = ops.empty() ? nullptr : ops[0].stream;
+    for (size_t i = next; i < ops.size(); ++i) {
+      if (used[i]) continue;
+      GroupOp &op = ops[i];
+      if (op.peer < 0 || op.peer >= n) return flagcxInvalidArgument;
+      if (op.isSend) {
+        if (a.sendSrc[op.peer]) continue; // slot of this peer is taken in this launch
+        a.sendSrc[op.peer] = (const char *)op.buf;
+        a.sendBytes[op.peer] = op.bytes;
+        if (!op.buf) a.sendSrc[op.peer] = (const char *)c->internalWin->local; // zero-byte message
+      } else {
+        if (a.recvDst[op.peer]) continue;
+        a.recvDst[op.peer] = (char *)op.buf;
+        a.recvBytes[op.peer] = op.bytes;
+        if (!op.buf) a.recvDst[op.peer] = (char *)c->internalWin->local;
+      }
+      used[i] = 1;
+      --remaining;
+    }
+    if (a.sendSrc[c->rank] && a.recvDst[c->rank] && a.sendBytes[c->rank] != a.recvBytes[c->rank]) {
+      FCX_WARN("send to self of %zu bytes meets a receive of %zu bytes", a.sendBytes[c->rank], a.recvBytes[c->rank]);
+      return flagcxInvalidArgument;
+    }
+    a.slotBytes = c->layout.p2pSlotBytes;
+    for (int p = 0; p < n; ++p) {
+      char *base = (char *)c->internalWin->peer[p];
+      a.stage[p] = base ? base + c->layout.p2pStageOff : nullptr;
+      a.ready[p] = base ? (unsigned long long *)(base + c->layout.p2pReadyOff) : nullptr;
+      a.done[p] = base ? (unsigned long long *)(base + c->layout.p2pDoneOff) : nullptr;
+      a.sendSeq[p] = c->p2pSendSeq[p];
+      a.recvSeq[p] = c->p2pRecvSeq[p];
+      if (p != c->rank) {
+        if (a.sendSrc[p]) c->p2pSendSeq[p] += (a.sendBytes[p] + a.slotBytes - 1) / a.slotBytes;
+        if (a.recvDst[p]) c->p2pRecvSeq[p] += (a.recvBytes[p] + a.slotBytes - 1) / a.slotBytes;
+      }
+    }
+    c->stats[flagcxCommOpSend].calls++;
+    if (c->emu) {
+      FCXCHECK(emuSubmit(c, 3, nullptr, &a, FLAGCX_P2P_CTAS, stream));
+    } else {
+      LaunchCtx lc;
+      lc.comm = &c->dev;
+      lc.stream = stream;
+      lc.nCtas = FLAGCX_P2P_CTAS;
+      cudaError_t e = launchP2pKernel(lc, a);
+      if (e != cudaSuccess) {
+        FCX_WARN("p2p kernel launch failed: %s", cudaGetErrorString(e));
+        return flagcxUnhandledDeviceError;
+      }
+    }
+  }
+  return flagcxSuccess;
+}
+
+} // namespace fcx

@@ -1,0 +1,49 @@
+// tuner.h -- picks the algorithm and CTA count of each device collective from
+// measured time.
+//
+// FlagCX's tuner (flagcx/core/flagcx_tuner.cc in the FlagCX project) searches NCCL
+// environment settings by re-creating NCCL communicators.  Here the search space
+// is this library's own algorithms x CTA counts; candidates are timed with CUDA
+// events (max over ranks), the winner per (operation, size bucket, registered or
+// staged) is kept with 5 % hysteresis against the built-in heuristic, and the
+// table can be saved to / loaded from JSON (FLAGCX_TUNE_FILE) so a job can skip
+// tuning.
+#pragma once
+#include <map>
+#include <string>
+
+#include "flagcx.h"
+#include "flagcx_ext.h"
+
+struct flagcxComm;
+
+namespace fcx {
+
+struct TuneChoice {
+  int algo = FLAGCX_ALGO_AUTO;
+  int nCtas = 0;
+  float usec = 0.f; // measured time of the winner (0: heuristic)
+};
+
+struct Tuner {
+  flagcxResult_t init(flagcxComm *c);
+  // registered: 1 when the buffers need no staging.  nvlsOk: multimem usable for
+  // this call.  Always returns a concrete algorithm and CTA count.
+  TuneChoice choose(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk) const;
+  TuneChoice heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk) const;
+  flagcxResult_t tune(flagcxComm *c, flagcxCommOp_t op, flagcxDataType_t dtype, size_t minBytes,
+                      size_t maxBytes, int iters);
+  flagcxResult_t save(const char *path) const;
+  flagcxResult_t load(const char *path);
+  std::string toJson() const;
+  flagcxResult_t fromJson(const std::string &text);
+
+  static int bucketOf(size_t bytes); // ceil(log2(bytes))
+  // key = op * 1000 + bucket * 2 + registered
+  std::map<int, TuneChoice> table;
+  int maxCtas = 32;
+  int forcedAlgo = FLAGCX_ALGO_AUTO; // FLAGCX_ALGO
+  int forcedCtas = 0;                // FLAGCX_NCTAS
+};
+
+} // namespace fcx

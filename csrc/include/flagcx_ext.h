@@ -1,0 +1,99 @@
+/*
+ * flagcx_ext.h -- entry points beyond the FlagCX-compatible surface of flagcx.h:
+ * collectives with a fused epilogue, explicit algorithm choice, the tuner,
+ * per-operation statistics, and the emulated world used to run multi-rank
+ * kernels on a single GPU.
+ */
+#ifndef FLAGCX_EXT_H_
+#define FLAGCX_EXT_H_
+#include "flagcx.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Algorithms of the device path.  FLAGCX_ALGO_AUTO lets the tuner decide. */
+typedef enum {
+  FLAGCX_ALGO_AUTO = -1,
+  FLAGCX_ALGO_ONESHOT = 0,      /* allreduce: every rank reduces all data from all peers */
+  FLAGCX_ALGO_TWOSHOT = 1,      /* allreduce: reduce own slice, write it to all peers */
+  FLAGCX_ALGO_NVLS_ONESHOT = 2, /* allreduce: multimem.ld_reduce everything */
+  FLAGCX_ALGO_NVLS_TWOSHOT = 3, /* allreduce: multimem.ld_reduce own slice + multimem.st */
+  FLAGCX_ALGO_PUSH = 4,         /* allgather/broadcast/alltoall: write into the peers' outputs */
+  FLAGCX_ALGO_PULL = 5,         /* reduce-scatter/allgather/...: read from the peers' inputs */
+  FLAGCX_ALGO_NVLS = 6,         /* reduce-scatter: multimem.ld_reduce; allgather: multimem.st */
+  FLAGCX_ALGO_COUNT = 7
+} flagcxAlgo_t;
+
+/* Optional work fused into the store of a reducing collective. */
+typedef struct {
+  float scale;               /* result multiplier; 1.0f for none (flagcxAvg already implies 1/nranks) */
+  flagcxDataType_t outDtype; /* flagcxNumTypes: same as input; flagcxFloat32 for 16-bit inputs;
+                                flagcxBfloat16 for fp32 inputs */
+  const void *residual;      /* added to the result (in the output type), or NULL */
+  int algo;                  /* flagcxAlgo_t or FLAGCX_ALGO_AUTO */
+  int nCtas;                 /* <=0: automatic */
+} flagcxFusedOpts_t;
+
+#define FLAGCX_FUSED_OPTS_INITIALIZER {1.0f, flagcxNumTypes, NULL, FLAGCX_ALGO_AUTO, 0}
+
+flagcxResult_t flagcxAllReduceFused(const void *sendbuff, void *recvbuff, size_t count,
+                                    flagcxDataType_t datatype, flagcxRedOp_t op,
+                                    const flagcxFusedOpts_t *opts, flagcxComm_t comm,
+                                    flagcxStream_t stream);
+flagcxResult_t flagcxReduceScatterFused(const void *sendbuff, void *recvbuff, size_t recvcount,
+                                        flagcxDataType_t datatype, flagcxRedOp_t op,
+                                        const flagcxFusedOpts_t *opts, flagcxComm_t comm,
+                                        flagcxStream_t stream);
+/* Non-reducing collectives with an explicit algorithm / CTA count. */
+flagcxResult_t flagcxAllGatherEx(const void *sendbuff, void *recvbuff, size_t sendcount,
+                                 flagcxDataType_t datatype, int algo, int nCtas, flagcxComm_t comm,
+                                 flagcxStream_t stream);
+
+/* ---- tuner ------------------------------------------------------------------ */
+/* Collective.  Measures every applicable (algorithm, CTA count) for `op` over the
+ * sizes minBytes..maxBytes (powers of two) on registered scratch buffers, keeps the
+ * fastest per size (max over ranks, CUDA events), and agrees on it across ranks. */
+flagcxResult_t flagcxTunerTune(flagcxComm_t comm, flagcxCommOp_t op, flagcxDataType_t dtype,
+                               size_t minBytes, size_t maxBytes, int iters);
+flagcxResult_t flagcxTunerSave(flagcxComm_t comm, const char *path);
+flagcxResult_t flagcxTunerLoad(flagcxComm_t comm, const char *path);
+/* What the tuner would pick. */
+flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, int registered,
+                                int *algo, int *nCtas);
+
+/* ---- statistics ----------------------------------------------------------------- */
+typedef struct {
+  uint64_t calls;
+  uint64_t bytes;
+  int lastAlgo;
+  int lastCtas;
+  float lastMs; /* device time of the last profiled call (0 when profiling is off) */
+} flagcxOpStats_t;
+flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOpStats_t *out);
+/* 1 when collectives on device buffers run as NVLink kernels, 0 on the socket path. */
+flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes);
+flagcxResult_t flagcxCommHasMulticast(flagcxComm_t comm, int *yes);
+/* Sets the bound of every device-side wait of this communicator. */
+flagcxResult_t flagcxCommSetWaitTimeoutMs(flagcxComm_t comm, int ms);
+/* Peer-mapped address of `offset` within a registered window as seen from this rank. */
+flagcxResult_t flagcxWindowGetPeerPointer(flagcxWindow_t win, int peer, size_t offset, void **ptr);
+flagcxResult_t flagcxWindowGetMulticastPointer(flagcxWindow_t win, size_t offset, void **ptr);
+
+/* ---- emulated world ----------------------------------------------------------------
+ * nranks communicators inside one process on one GPU.  A collective call on one
+ * of them is parked until all of them have made the matching call; the last call
+ * launches ONE cooperative kernel in which blockIdx.y plays the rank, so the
+ * multi-rank protocols (barriers, peer loads/stores) run unchanged on a single
+ * GPU.  Buffers of emulated ranks see each other without registration. */
+flagcxResult_t flagcxEmuWorldCreate(int nranks, int device, flagcxComm_t *comms);
+flagcxResult_t flagcxEmuWorldDestroy(flagcxComm_t anyRank);
+
+/* Host-side element-wise reduction used by the socket path (exposed for tests). */
+flagcxResult_t flagcxHostReduce(void *dst, const void *src, size_t count, flagcxDataType_t dtype,
+                                flagcxRedOp_t op);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

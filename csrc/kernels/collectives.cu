@@ -1,0 +1,675 @@
+// collectives.cu -- the sm_100a collective kernels and their launch table.
+//
+// Every collective of the device path is ONE kernel launch per rank.  The kernel
+// reads and writes the other ranks' buffers directly through their NVLink peer
+// mappings; ranks meet only at per-CTA barriers made of release/acquire flags in
+// peer memory (flagcx_device.cuh).  The adjacent element-wise work -- scaling
+// (average, 1/world), bf16<->fp32 conversion of the result, a residual add -- is
+// applied to the accumulator in registers before the single store.
+//
+// These kernels take the place of the FlagCX custom all-reduce kernels
+// (flagcx/adaptor/kernel/nvidia/custom_allreduce.cu:337-467 in the FlagCX project:
+// one-shot peer reduce, NVLS one-shot and NVLS two-shot) and of every NCCL call of
+// its NCCL adaptor (flagcx/adaptor/ccl/nccl_adaptor.cc:228-382).  Differences:
+// 16-byte accesses, fp32 accumulation in a fixed rank order (all ranks get
+// bit-identical results), no staging copy when the buffers are registered, no
+// size cap, all reductions and element types, and waits that give up with an
+// error status instead of spinning forever.
+#include <cuda_runtime.h>
+
+#include "launch.h"
+#include "prims.cuh"
+
+namespace fcx {
+namespace {
+
+// ---------------------------------------------------------------------------
+// copy-in / copy-out between user buffers and the peer-visible staging
+// ---------------------------------------------------------------------------
+// nBlocks blocks of blockBytes; block j is read at src + j*srcStride and written
+// at dst + j*dstStride.  This CTA moves its share of every block, so what CTA b
+// stages is exactly what CTA b of a peer consumes.
+__device__ void ctaCopyBlocks(char *dst, size_t dstStride, const char *src, size_t srcStride, int nBlocks,
+                              size_t blockBytes, size_t totalBytes, int b, int g) {
+  if (blockBytes == 0) return;
+  for (int j = 0; j < nBlocks; ++j) {
+    size_t len = blockBytes;
+    if (totalBytes) { // back-to-back blocks, the last may be short or empty
+      size_t start = (size_t)j * blockBytes;
+      if (start >= totalBytes) break;
+      if (totalBytes - start < len) len = totalBytes - start;
+    }
+    size_t ub, ue;
+    ctaShare((len + 15) >> 4, b, g, &ub, &ue);
+    size_t bb = ub << 4, be = (ue << 4) < len ? (ue << 4) : len;
+    ctaCopy(dst + j * dstStride, src + j * srcStride, bb, be);
+  }
+}
+
+__device__ __forceinline__ void copyIn(const CollArgs &a, int rank, int b, int g) {
+  if (!a.userIn) return;
+  size_t stageStride = a.inStride ? a.inStride : a.inBlockBytes;
+  ctaCopyBlocks((char *)a.in[rank], stageStride, a.userIn, a.userInStride, a.nInBlocks, a.inBlockBytes,
+                a.inTotalBytes, b, g);
+}
+__device__ __forceinline__ void copyOut(const CollArgs &a, int rank, int b, int g) {
+  if (!a.userOut) return;
+  size_t stageStride = a.outStride ? a.outStride : a.outBlockBytes;
+  ctaCopyBlocks(a.userOut, a.userOutStride, a.out[rank], stageStride, a.nOutBlocks, a.outBlockBytes,
+                a.outTotalBytes, b, g);
+}
+
+// ---------------------------------------------------------------------------
+// reduce family
+// ---------------------------------------------------------------------------
+template <typename T, int OP, int NR>
+struct Reducer {
+  using Acc = typename Elem<T>::Acc;
+  static constexpr int N = 16 / (int)sizeof(T);
+
+  // Reduces the 16-byte pack at byte offset `off` of every rank's input, always in
+  // rank order 0..n-1 so that every rank computes bit-identical sums.
+  static __device__ __forceinline__ void loadReduce(const CollArgs &a, int nRanks, size_t off, Acc (&acc)[N]) {
+    uint4 v[FLAGCX_MAX_RANKS];
+    if (NR > 0) {
+#pragma unroll
+      for (int p = 0; p < NR; ++p) v[p] = ldSys16(a.in[p] + off);
+    } else {
+#pragma unroll
+      for (int p = 0; p < FLAGCX_MAX_RANKS; ++p)
+        if (p < nRanks) v[p] = ldSys16(a.in[p] + off);
+    }
+    const T *e0 = (const T *)&v[0];
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] = toAcc<T>(e0[i]);
+#pragma unroll
+    for (int p = 1; p < (NR > 0 ? NR : FLAGCX_MAX_RANKS); ++p) {
+      if (NR > 0 || p < nRanks) {
+        const T *e = (const T *)&v[p];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = combine<OP, Acc>(acc[i], toAcc<T>(e[i]), a.redOp);
+      }
+    }
+  }
+
+  // Applies the epilogue and stores one pack at element index `e` (relative to
+  // each destination base) to nDst destinations.
+  static __device__ __forceinline__ void storePack(const CollArgs &a, char *const *dst, int nDst, size_t e,
+                                                   Acc (&acc)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] = finish<Acc>(acc[i], a.scale, a.divisor);
+    if constexpr (sizeof(T) == 2) {
+      if (a.outMode == kOutFloat) { // 8 x 16-bit in, 8 x fp32 out
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (float)acc[i];
+        if (a.residual) {
+          const float *r = (const float *)a.residual + e;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] += r[i];
+        }
+        for (int d = 0; d < nDst; ++d) {
+          float *o = (float *)dst[d] + e;
+          st16(o, *(uint4 *)&f[0]);
+          st16(o + 4, *(uint4 *)&f[4]);
+        }
+        return;
+      }
+    }
+    if constexpr (sizeof(T) == 4) {
+      if (a.outMode == kOutBf16) { // 4 x fp32 in, 4 x bf16 out
+        __align__(8) __nv_bfloat16 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float x = (float)acc[i];
+          if (a.residual) x += __bfloat162float(((const __nv_bfloat16 *)a.residual)[e + i]);
+          h[i] = __float2bfloat16_rn(x);
+        }
+        for (int d = 0; d < nDst; ++d) *(uint2 *)((__nv_bfloat16 *)dst[d] + e) = *(uint2 *)h;
+        return;
+      }
+    }
+    uint4 o;
+    T *oe = (T *)&o;
+    if (a.residual) {
+      uint4 rv = ldLocal16((const T *)a.residual + e);
+      const T *re = (const T *)&rv;
+#pragma unroll
+      for (int i = 0; i < N; ++i) oe[i] = fromAcc<T>(acc[i] + toAcc<T>(re[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) oe[i] = fromAcc<T>(acc[i]);
+    }
+    for (int d = 0; d < nDst; ++d) st16((T *)dst[d] + e, o);
+  }
+
+  static __device__ __forceinline__ void storeOne(const CollArgs &a, char *const *dst, int nDst, size_t e, Acc v) {
+    v = finish<Acc>(v, a.scale, a.divisor);
+    for (int d = 0; d < nDst; ++d) {
+      if (a.outMode == kOutFloat && sizeof(T) == 2) {
+        float x = (float)v;
+        if (a.residual) x += ((const float *)a.residual)[e];
+        ((float *)dst[d])[e] = x;
+      } else if (a.outMode == kOutBf16 && sizeof(T) == 4) {
+        float x = (float)v;
+        if (a.residual) x += __bfloat162float(((const __nv_bfloat16 *)a.residual)[e]);
+        ((__nv_bfloat16 *)dst[d])[e] = __float2bfloat16_rn(x);
+      } else {
+        Acc x = v;
+        if (a.residual) x = x + toAcc<T>(((const T *)a.residual)[e]);
+        ((T *)dst[d])[e] = fromAcc<T>(x);
+      }
+    }
+  }
+
+  // Reduces elements [sb, se) of the inputs (indices into in[p]) and stores them at
+  // element index (i - sb + dstBase) of each destination.  The CTA takes its share
+  // of the range in 16-byte units.
+  static __device__ void slice(const CollArgs &a, int nRanks, size_t sb, size_t se, char *const *dst, int nDst,
+                               size_t dstBase, int b, int g) {
+    if (se <= sb) return;
+    const size_t elems = se - sb;
+    const size_t outSize = a.outMode == kOutFloat ? 4 : (a.outMode == kOutBf16 ? 2 : sizeof(T));
+    bool vec = ((sb * sizeof(T)) & 15) == 0 && ((dstBase * outSize) & 15) == 0;
+    for (int p = 0; p < nRanks; ++p) vec &= (((uintptr_t)a.in[p]) & 15) == 0;
+    for (int d = 0; d < nDst; ++d) vec &= (((uintptr_t)dst[d]) & 15) == 0;
+    if (a.residual) vec &= (((uintptr_t)a.residual) & 15) == 0;
+    size_t ub, ue;
+    ctaShare((elems * sizeof(T) + 15) >> 4, b, g, &ub, &ue);
+    size_t eb = ub * N, ee = ue * N < elems ? ue * N : elems; // this CTA's elements, relative to sb
+    if (vec) {
+      const size_t fullEnd = ee / N * N; // whole packs only
+      for (size_t e = eb + (size_t)threadIdx.x * N; e < fullEnd; e += (size_t)blockDim.x * N) {
+        Acc acc[N];
+        loadReduce(a, nRanks, (sb + e) * sizeof(T), acc);
+        storePack(a, dst, nDst, dstBase + e, acc);
+      }
+      eb = fullEnd > eb ? fullEnd : eb;
+    }
+    for (size_t e = eb + threadIdx.x; e < ee; e += blockDim.x) {
+      Acc acc = toAcc<T>(ldSysElem((const T *)a.in[0] + sb + e));
+      for (int p = 1; p < nRanks; ++p)
+        acc = combine<OP, Acc>(acc, toAcc<T>(ldSysElem((const T *)a.in[p] + sb + e)), a.redOp);
+      storeOne(a, dst, nDst, dstBase + e, acc);
+    }
+  }
+};
+
+template <typename T, int OP, int NR>
+__device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
+  const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
+  using R = Reducer<T, OP, NR>;
+
+  copyIn(a, rank, b, g);
+  if (a.flags & kFlagBeginBarrier)
+    if (!ctaBarrier(c, b)) return;
+
+  char *local[1] = {a.out[rank]};
+  switch (a.kind) {
+    case kAllReduceOneShot:
+      R::slice(a, n, 0, a.count, local, 1, 0, b, g);
+      break;
+    case kAllReduceTwoShot: {
+      size_t s = sliceElems(a.count, n, sizeof(T));
+      size_t sb = s * rank < a.count ? s * rank : a.count;
+      size_t se = sb + s < a.count ? sb + s : a.count;
+      R::slice(a, n, sb, se, a.out, n, sb, b, g);
+      break;
+    }
+    case kReduceScatter: {
+      size_t sb = a.inStride / sizeof(T) * rank;
+      R::slice(a, n, sb, sb + a.count, local, 1, 0, b, g);
+      break;
+    }
+    case kReduceToRoot:
+      if (rank == a.root) R::slice(a, n, 0, a.count, local, 1, 0, b, g);
+      break;
+    default: break;
+  }
+
+  if (a.flags & kFlagEndBarrier)
+    if (!ctaBarrier(c, b)) return;
+  copyOut(a, rank, b, g);
+}
+
+template <typename T, int OP, int NR>
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    reduceKernel(const flagcxDevComm c, const CollArgs a) {
+  reduceBody<T, OP, NR>(c, a);
+}
+
+// Emulated world: one cooperative launch, blockIdx.y plays the rank.
+template <typename T, int OP, int NR>
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    reduceKernelEmu(const flagcxDevComm *cs, const CollArgs *as) {
+  reduceBody<T, OP, NR>(cs[blockIdx.y], as[blockIdx.y]);
+}
+
+// ---------------------------------------------------------------------------
+// copy family (no arithmetic: byte movers)
+// ---------------------------------------------------------------------------
+// One read of the source, one store per destination.
+__device__ void ctaFanOut(char *const *dst, int nDst, const char *src, size_t bytes, int b, int g) {
+  size_t ub, ue;
+  ctaShare((bytes + 15) >> 4, b, g, &ub, &ue);
+  size_t bb = ub << 4, be = (ue << 4) < bytes ? (ue << 4) : bytes;
+  if (bb >= be) return;
+  bool vec = (((uintptr_t)src) & 15) == 0;
+  for (int d = 0; d < nDst; ++d) vec &= (((uintptr_t)dst[d]) & 15) == 0;
+  const int t = threadIdx.x, nt = blockDim.x;
+  size_t done = bb;
+  if (vec) {
+    size_t ve = be >> 4;
+    size_t i = ub + t;
+    for (; i + nt < ve; i += 2 * (size_t)nt) {
+      uint4 v0 = ldSys16(src + (i << 4)), v1 = ldSys16(src + ((i + nt) << 4));
+      for (int d = 0; d < nDst; ++d) {
+        st16(dst[d] + (i << 4), v0);
+        st16(dst[d] + ((i + nt) << 4), v1);
+      }
+    }
+    for (; i < ve; i += nt) {
+      uint4 v = ldSys16(src + (i << 4));
+      for (int d = 0; d < nDst; ++d) st16(dst[d] + (i << 4), v);
+    }
+    done = ve > ub ? (ve << 4) : bb;
+  }
+  for (size_t i = done + t; i < be; i += nt) {
+    char v = src[i];
+    for (int d = 0; d < nDst; ++d) dst[d][i] = v;
+  }
+}
+
+__device__ void ctaCopyShare(char *dst, const char *src, size_t bytes, int b, int g) {
+  size_t ub, ue;
+  ctaShare((bytes + 15) >> 4, b, g, &ub, &ue);
+  size_t bb = ub << 4, be = (ue << 4) < bytes ? (ue << 4) : bytes;
+  ctaCopy(dst, src, bb, be);
+}
+
+__device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
+  const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
+  const size_t es = a.elemSize;
+  const size_t blk = a.count * es;
+
+  if (a.kind == kAllToAllvPull) {
+    // publish where each peer finds its block in my input (every CTA writes the
+    // same values: its peers' CTAs of the same index read them after the barrier)
+    unsigned long long *m = a.meta[rank];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      m[i] = a.sendDispls[i];
+      m[FLAGCX_MAX_RANKS + i] = a.sendCounts[i];
+    }
+  }
+  copyIn(a, rank, b, g);
+  if (a.flags & kFlagBeginBarrier)
+    if (!ctaBarrier(c, b)) return;
+
+  switch (a.kind) {
+    case kAllGatherPush: {
+      char *dst[FLAGCX_MAX_RANKS];
+      int nd = 0;
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        char *d = a.out[p] + a.outStride * rank;
+        if (p == rank && d == a.in[rank]) continue; // in place
+        dst[nd++] = d;
+      }
+      ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+      break;
+    }
+    case kAllGatherPull:
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        char *d = a.out[rank] + a.outStride * p;
+        if (p == rank && a.in[p] == d) continue;
+        ctaCopyShare(d, a.in[p], blk, b, g);
+      }
+      break;
+    case kBroadcastPush:
+      if (rank == a.root) {
+        char *dst[FLAGCX_MAX_RANKS];
+        int nd = 0;
+        for (int k = 0; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          if (p == rank && a.in[rank] == a.out[rank]) continue;
+          dst[nd++] = a.out[p];
+        }
+        ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+      }
+      break;
+    case kBroadcastPull:
+      if (!(rank == a.root && a.in[rank] == a.out[rank])) ctaCopyShare(a.out[rank], a.in[a.root], blk, b, g);
+      break;
+    case kGatherPull:
+      if (rank == a.root)
+        for (int k = 0; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          ctaCopyShare(a.out[rank] + a.outStride * p, a.in[p], blk, b, g);
+        }
+      break;
+    case kScatterPull:
+      ctaCopyShare(a.out[rank], a.in[a.root] + a.inStride * rank, blk, b, g);
+      break;
+    case kAllToAllPush:
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        ctaCopyShare(a.out[p] + a.outStride * rank, a.in[rank] + a.inStride * p, blk, b, g);
+      }
+      break;
+    case kAllToAllPull:
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        ctaCopyShare(a.out[rank] + a.outStride * p, a.in[p] + a.inStride * rank, blk, b, g);
+      }
+      break;
+    case kAllToAllvPull:
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        unsigned long long displ = fcxdev::ldRelaxedSys(a.meta[p] + rank);
+        unsigned long long cnt = fcxdev::ldRelaxedSys(a.meta[p] + FLAGCX_MAX_RANKS + rank);
+        if (cnt != a.recvCounts[p]) {
+          if (threadIdx.x == 0 && b == 0)
+            fcxdev::reportError(c.status, FLAGCX_DEV_BOUNDS, FLAGCX_DEV_AT_KERNEL, (unsigned)p, cnt);
+          continue;
+        }
+        ctaCopyShare(a.out[rank] + a.recvDispls[p] * es, a.in[p] + displ * es, cnt * es, b, g);
+      }
+      break;
+    default: break;
+  }
+
+  if (a.flags & kFlagEndBarrier)
+    if (!ctaBarrier(c, b)) return;
+  copyOut(a, rank, b, g);
+}
+
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) copyKernel(const flagcxDevComm c, const CollArgs a) {
+  copyBody(c, a);
+}
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    copyKernelEmu(const flagcxDevComm *cs, const CollArgs *as) {
+  copyBody(cs[blockIdx.y], as[blockIdx.y]);
+}
+
+// ---------------------------------------------------------------------------
+// grouped point-to-point (see P2pArgs)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool ctaWaitFlag(const flagcxDevComm &c, const unsigned long long *flag,
+                                            unsigned long long want, unsigned peer) {
+  bool ok = true;
+  if (threadIdx.x == 0) ok = fcxdev::waitGe(c, flag, want, FLAGCX_DEV_AT_SIGNAL, peer);
+  return !__syncthreads_or(ok ? 0 : 1);
+}
+__device__ __forceinline__ void ctaRaiseFlag(unsigned long long *flag, unsigned long long v) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fcxdev::fenceSys();
+    fcxdev::stReleaseSys(flag, v);
+  }
+}
+
+__device__ void p2pBody(const flagcxDevComm &c, const P2pArgs &a) {
+  const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
+  const size_t slot = a.slotBytes;
+  if (a.sendSrc[rank] && a.recvDst[rank] && a.sendBytes[rank])
+    ctaCopyShare(a.recvDst[rank], a.sendSrc[rank], a.sendBytes[rank], b, g);
+  size_t maxIter = 0;
+  for (int p = 0; p < n; ++p) {
+    if (p == rank) continue;
+    size_t s = a.sendSrc[p] ? (a.sendBytes[p] + slot - 1) / slot : 0;
+    size_t r = a.recvDst[p] ? (a.recvBytes[p] + slot - 1) / slot : 0;
+    maxIter = s > maxIter ? s : maxIter;
+    maxIter = r > maxIter ? r : maxIter;
+  }
+  for (size_t i = 0; i < maxIter; ++i) {
+    for (int k = 1; k < n; ++k) { // sends of this step
+      int p = rank + k; if (p >= n) p -= n;
+      if (!a.sendSrc[p] || i * slot >= a.sendBytes[p]) continue;
+      size_t len = a.sendBytes[p] - i * slot < slot ? a.sendBytes[p] - i * slot : slot;
+      unsigned long long seq = a.sendSeq[p] + i + 1;
+      // the receiver must have drained the previous chunk out of this slot
+      if (!ctaWaitFlag(c, a.done[rank] + p * FLAGCX_P2P_CTAS + b, seq - 1, (unsigned)p)) return;
+      ctaCopyShare(a.stage[rank] + slot * p, a.sendSrc[p] + i * slot, len, b, g);
+      ctaRaiseFlag(a.ready[p] + rank * FLAGCX_P2P_CTAS + b, seq);
+    }
+    for (int k = 1; k < n; ++k) { // receives of this step
+      int p = rank - k; if (p < 0) p += n;
+      if (!a.recvDst[p] || i * slot >= a.recvBytes[p]) continue;
+      size_t len = a.recvBytes[p] - i * slot < slot ? a.recvBytes[p] - i * slot : slot;
+      unsigned long long seq = a.recvSeq[p] + i + 1;
+      if (!ctaWaitFlag(c, a.ready[rank] + p * FLAGCX_P2P_CTAS + b, seq, (unsigned)p)) return;
+      ctaCopyShare(a.recvDst[p] + i * slot, a.stage[p] + slot * rank, len, b, g);
+      ctaRaiseFlag(a.done[p] + rank * FLAGCX_P2P_CTAS + b, seq);
+    }
+  }
+}
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) p2pKernel(const flagcxDevComm c, const P2pArgs a) {
+  p2pBody(c, a);
+}
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    p2pKernelEmu(const flagcxDevComm *cs, const P2pArgs *as) {
+  p2pBody(cs[blockIdx.y], as[blockIdx.y]);
+}
+
+// ---------------------------------------------------------------------------
+// NVLS family: the switch reduces (multimem.ld_reduce) and broadcasts (multimem.st)
+// ---------------------------------------------------------------------------
+template <typename T> struct Mm;
+template <> struct Mm<float> {
+  // the switch adds fp32 but has no fp32 min/max; the host never routes those here
+  static __device__ __forceinline__ uint4 ldReduce(const void *p, int) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void *p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Mm<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ldReduce(const void *p, int op) {
+    uint4 v;
+    if (op == kOpMin)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.min.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else if (op == kOpMax)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.max.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void *p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Mm<__half> {
+  static __device__ __forceinline__ uint4 ldReduce(const void *p, int op) {
+    uint4 v;
+    if (op == kOpMin)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.min.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else if (op == kOpMax)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.max.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void *p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ uint4 scalePack(uint4 v, float scale) {
+  if (scale == 1.0f) return v;
+  constexpr int N = 16 / (int)sizeof(T);
+  T *e = (T *)&v;
+#pragma unroll
+  for (int i = 0; i < N; ++i) e[i] = fromAcc<T>(toAcc<T>(e[i]) * scale);
+  return v;
+}
+
+// All sizes here are whole 16-byte packs (the host falls back otherwise).
+template <typename T>
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) nvlsKernel(const flagcxDevComm c, const CollArgs a) {
+  const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
+  constexpr int N = 16 / (int)sizeof(T);
+  const int t = threadIdx.x, nt = blockDim.x;
+  copyIn(a, rank, b, g);
+  if (a.flags & kFlagBeginBarrier)
+    if (!ctaBarrier(c, b)) return;
+  size_t ub, ue;
+  switch (a.kind) {
+    case kAllReduceNvlsOneShot: {
+      ctaShare(a.count / N, b, g, &ub, &ue);
+      for (size_t i = ub + t; i < ue; i += nt) {
+        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp), a.scale);
+        st16(a.out[rank] + (i << 4), v);
+      }
+      break;
+    }
+    case kAllReduceNvlsTwoShot: {
+      size_t s = sliceElems(a.count, n, sizeof(T));
+      size_t sb = s * rank < a.count ? s * rank : a.count;
+      size_t se = sb + s < a.count ? sb + s : a.count;
+      ctaShare((se - sb) / N, b, g, &ub, &ue);
+      size_t base = sb / N;
+      size_t i = base + ub + t;
+      for (; i + nt < base + ue; i += 2 * (size_t)nt) {
+        uint4 v0 = Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp);
+        uint4 v1 = Mm<T>::ldReduce(a.mcIn + ((i + nt) << 4), a.redOp);
+        Mm<T>::st(a.mcOut + (i << 4), scalePack<T>(v0, a.scale));
+        Mm<T>::st(a.mcOut + ((i + nt) << 4), scalePack<T>(v1, a.scale));
+      }
+      for (; i < base + ue; i += nt) {
+        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp), a.scale);
+        Mm<T>::st(a.mcOut + (i << 4), v);
+      }
+      break;
+    }
+    case kReduceScatterNvls: {
+      ctaShare(a.count / N, b, g, &ub, &ue);
+      size_t base = a.inStride * rank >> 4;
+      for (size_t i = ub + t; i < ue; i += nt) {
+        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + ((base + i) << 4), a.redOp), a.scale);
+        st16(a.out[rank] + (i << 4), v);
+      }
+      break;
+    }
+    case kAllGatherNvls: {
+      ctaShare(a.count / N, b, g, &ub, &ue);
+      size_t base = a.outStride * rank >> 4;
+      for (size_t i = ub + t; i < ue; i += nt) {
+        uint4 v = ldSys16(a.in[rank] + (i << 4));
+        Mm<T>::st(a.mcOut + ((base + i) << 4), v);
+      }
+      break;
+    }
+    default: break;
+  }
+  if (a.flags & kFlagEndBarrier)
+    if (!ctaBarrier(c, b)) return;
+  copyOut(a, rank, b, g);
+}
+
+// ---------------------------------------------------------------------------
+// dispatch
+// ---------------------------------------------------------------------------
+template <typename T, int OP, int NR>
+cudaError_t launchReduceT(const LaunchCtx &lc, const CollArgs &a) {
+  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  if (lc.emuRanks > 0) {
+    void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
+    return cudaLaunchCooperativeKernel((const void *)reduceKernelEmu<T, OP, NR>, grid, block, params, 0, lc.stream);
+  }
+  reduceKernel<T, OP, NR><<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launchReduceHot(const LaunchCtx &lc, const CollArgs &a, int nRanks) {
+  // sum (and average, which is sum with a scale) at the common world sizes get the
+  // fully unrolled instantiation; everything else takes the generic one
+  if (a.redOp == kOpSum) {
+    switch (nRanks) {
+      case 2: return launchReduceT<T, kOpSum, 2>(lc, a);
+      case 4: return launchReduceT<T, kOpSum, 4>(lc, a);
+      case 8: return launchReduceT<T, kOpSum, 8>(lc, a);
+      default: break;
+    }
+  }
+  return launchReduceT<T, kOpRuntime, 0>(lc, a);
+}
+
+} // namespace
+
+cudaError_t launchReduceKernel(const LaunchCtx &lc, const CollArgs &a, int nRanks) {
+  switch ((flagcxDataType_t)a.dtype) {
+    case flagcxFloat32: return launchReduceHot<float>(lc, a, nRanks);
+    case flagcxBfloat16: return launchReduceHot<__nv_bfloat16>(lc, a, nRanks);
+    case flagcxFloat16: return launchReduceHot<__half>(lc, a, nRanks);
+    case flagcxFloat64: return launchReduceT<double, kOpRuntime, 0>(lc, a);
+    case flagcxInt8: return launchReduceT<signed char, kOpRuntime, 0>(lc, a);
+    case flagcxUint8: return launchReduceT<unsigned char, kOpRuntime, 0>(lc, a);
+    case flagcxInt32: return launchReduceT<int, kOpRuntime, 0>(lc, a);
+    case flagcxUint32: return launchReduceT<unsigned int, kOpRuntime, 0>(lc, a);
+    case flagcxInt64: return launchReduceT<long long, kOpRuntime, 0>(lc, a);
+    case flagcxUint64: return launchReduceT<unsigned long long, kOpRuntime, 0>(lc, a);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a) {
+  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  if (lc.emuRanks > 0) {
+    void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
+    return cudaLaunchCooperativeKernel((const void *)copyKernelEmu, grid, block, params, 0, lc.stream);
+  }
+  copyKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launchP2pKernel(const LaunchCtx &lc, const P2pArgs &a) {
+  dim3 grid(FLAGCX_P2P_CTAS, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  if (lc.emuRanks > 0) {
+    void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuP2p};
+    return cudaLaunchCooperativeKernel((const void *)p2pKernelEmu, grid, block, params, 0, lc.stream);
+  }
+  p2pKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launchNvlsKernel(const LaunchCtx &lc, const CollArgs &a) {
+  if (lc.emuRanks > 0) return cudaErrorNotSupported; // multimem needs a real multicast object
+  dim3 grid(lc.nCtas), block(lc.nThreads);
+  switch ((flagcxDataType_t)a.dtype) {
+    case flagcxFloat32: nvlsKernel<float><<<grid, block, 0, lc.stream>>>(*lc.comm, a); break;
+    case flagcxBfloat16: nvlsKernel<__nv_bfloat16><<<grid, block, 0, lc.stream>>>(*lc.comm, a); break;
+    case flagcxFloat16: nvlsKernel<__half><<<grid, block, 0, lc.stream>>>(*lc.comm, a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+int maxCoresidentCtas(int nThreads) {
+  int dev = 0, sms = 0, perSm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, (const void *)copyKernelEmu, nThreads, 0);
+  int reduceOcc = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reduceOcc, (const void *)reduceKernelEmu<double, kOpRuntime, 0>,
+                                                nThreads, 0);
+  if (reduceOcc < perSm) perSm = reduceOcc;
+  return sms * (perSm > 0 ? perSm : 1);
+}
+
+} // namespace fcx
