@@ -102,7 +102,7 @@ flagcxResult_t setReduceEpilogue(flagcxComm *c, CollArgs &a, const DeviceCollReq
   a.scale = rq.scale;
   a.divisor = 0;
   if (rq.redOp == flagcxAvg) {
-    if (isFloatType(rq.dtype)) a.scale *= 1.0f / (float)c->nranks;
+    if (isFloatType(rq.dtype) && rq.dtype != flagcxFloat64) a.scale *= 1.0f / (float)c->nranks;
     else a.divisor = c->nranks;
   }
   a.outMode = kOutSame;

@@ -669,7 +669,9 @@ int maxCoresidentCtas(int nThreads) {
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&reduceOcc, (const void *)reduceKernelEmu<double, kOpRuntime, 0>,
                                                 nThreads, 0);
   if (reduceOcc < perSm) perSm = reduceOcc;
-  return sms * (perSm > 0 ? perSm : 1);
+  // other instantiations may fit fewer blocks per SM than these two: count one
+  // per SM so that the cooperative launch is accepted for all of them
+  return sms * (perSm > 0 ? 1 : 0);
 }
 
 } // namespace fcx

@@ -90,7 +90,11 @@ template <typename A> __device__ __forceinline__ A finish(A v, float scale, int 
   return divisor ? (A)(v / (A)divisor) : v;
 }
 template <> __device__ __forceinline__ float finish<float>(float v, float scale, int) { return v * scale; }
-template <> __device__ __forceinline__ double finish<double>(double v, float scale, int) { return v * (double)scale; }
+// double keeps its precision: the average divides exactly instead of using the fp32 scale
+template <> __device__ __forceinline__ double finish<double>(double v, float scale, int divisor) {
+  if (divisor) v /= (double)divisor;
+  return scale == 1.0f ? v : v * (double)scale;
+}
 
 // ---- partitioning ---------------------------------------------------------------------
 // Contiguous share of [0, n) that CTA `b` of `g` owns.  Every rank computes the same

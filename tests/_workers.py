@@ -1,0 +1,293 @@
+"""Rank bodies for the multi-process tests (imported by name in spawned children)."""
+import os
+import time
+
+import numpy as np
+
+from flagcx_b200 import capi
+
+NP_TYPES = {
+    capi.INT8: np.int8, capi.UINT8: np.uint8, capi.INT32: np.int32, capi.UINT32: np.uint32,
+    capi.INT64: np.int64, capi.UINT64: np.uint64, capi.HALF: np.float16, capi.FLOAT: np.float32,
+    capi.DOUBLE: np.float64,
+}
+
+
+def seeded(rank, n, dtype_code):
+    """Values uniform in [-1, 1) from seed=rank (small integers for integer types)."""
+    rng = np.random.default_rng(rank)
+    npdt = NP_TYPES[dtype_code]
+    if np.issubdtype(npdt, np.floating):
+        return rng.uniform(-1, 1, n).astype(npdt)
+    if np.issubdtype(npdt, np.unsignedinteger):
+        return rng.integers(0, 3, n).astype(npdt)
+    return rng.integers(-2, 3, n).astype(npdt)
+
+
+def np_reduce(arrs, op):
+    acc = np.stack(arrs).astype(np.float64)
+    if op == capi.SUM:
+        return acc.sum(0)
+    if op == capi.PROD:
+        return acc.prod(0)
+    if op == capi.MAX:
+        return acc.max(0)
+    if op == capi.MIN:
+        return acc.min(0)
+    if op == capi.AVG:
+        return acc.sum(0) / len(arrs)
+    raise ValueError(op)
+
+
+def rel_err(got, ref):
+    got = np.asarray(got, np.float64)
+    return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)))
+
+
+def host_collectives(rank, n, uid, count, dtype_code):
+    """BASELINE config 1: allreduce / allgather / reducescatter / alltoall / send-recv
+    on host buffers, checked against numpy."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    assert comm.rank == rank and comm.nranks == n
+    xs = [seeded(r, count, dtype_code) for r in range(n)]
+    x = xs[rank]
+    out = {}
+    ar = np.empty_like(x)
+    comm.all_reduce(x, ar, count, dtype_code, capi.SUM)
+    out["allreduce"] = rel_err(ar, np_reduce(xs, capi.SUM))
+    ag = np.empty(count * n, x.dtype)
+    comm.all_gather(x, ag, count, dtype_code)
+    out["allgather"] = float(not np.array_equal(ag, np.concatenate(xs)))
+    per = count // n
+    rs = np.empty(per, x.dtype)
+    comm.reduce_scatter(x, rs, per, dtype_code, capi.SUM)
+    out["reducescatter"] = rel_err(rs, np_reduce([a[: per * n] for a in xs], capi.SUM)[rank * per:(rank + 1) * per])
+    a2a = np.empty(per * n, x.dtype)
+    comm.all_to_all(x, a2a, per, dtype_code)
+    exp = np.concatenate([xs[p][rank * per:(rank + 1) * per] for p in range(n)])
+    out["alltoall"] = float(not np.array_equal(a2a, exp))
+    # ring send/recv inside a group
+    nxt, prv = (rank + 1) % n, (rank - 1 + n) % n
+    got = np.empty_like(x)
+    comm.group_start()
+    comm.send(x, count, dtype_code, nxt)
+    comm.recv(got, count, dtype_code, prv)
+    comm.group_end()
+    out["sendrecv"] = float(not np.array_equal(got, xs[prv]))
+    comm.barrier()
+    comm.destroy()
+    return out
+
+
+def host_all_ops(rank, n, uid, count):
+    """Every collective, several dtypes and reductions, odd counts."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    worst = 0.0
+    for dt in (capi.FLOAT, capi.DOUBLE, capi.INT32, capi.INT64, capi.UINT8, capi.HALF):
+        xs = [seeded(r, count, dt) for r in range(n)]
+        x = xs[rank]
+        for op in (capi.SUM, capi.PROD, capi.MAX, capi.MIN, capi.AVG):
+            if op == capi.AVG and not np.issubdtype(x.dtype, np.floating):
+                continue
+            ar = np.empty_like(x)
+            comm.all_reduce(x, ar, count, dt, op)
+            tol_scale = 1e-2 if dt == capi.HALF else 1.0
+            worst = max(worst, rel_err(ar, np_reduce(xs, op)) * tol_scale)
+            root = (n - 1) if n > 1 else 0
+            rd = np.zeros_like(x)
+            comm.reduce(x, rd, count, dt, op, root)
+            if rank == root:
+                worst = max(worst, rel_err(rd, np_reduce(xs, op)) * tol_scale)
+        # in place
+        ip = x.copy()
+        comm.all_reduce(ip, ip, count, dt, capi.MAX)
+        worst = max(worst, rel_err(ip, np_reduce(xs, capi.MAX)))
+        root = 0
+        b = x.copy() if rank == root else np.zeros_like(x)
+        comm.broadcast(b, b, count, dt, root)
+        assert np.array_equal(b, xs[root]), "broadcast"
+        g = np.zeros(count * n, x.dtype)
+        comm.gather(x, g, count, dt, root)
+        if rank == root:
+            assert np.array_equal(g, np.concatenate(xs)), "gather"
+        src = np.concatenate(xs) if rank == root else np.zeros(count * n, x.dtype)
+        sc = np.zeros(count, x.dtype)
+        comm.scatter(src, sc, count, dt, root)
+        assert np.array_equal(sc, xs[rank]), "scatter"
+    # alltoallv with rank-dependent counts
+    dt = capi.FLOAT
+    scounts = [(rank + p) % 5 + 1 for p in range(n)]
+    rcounts = [(p + rank) % 5 + 1 for p in range(n)]
+    sdispls = np.concatenate([[0], np.cumsum(scounts)[:-1]]).tolist()
+    rdispls = np.concatenate([[0], np.cumsum(rcounts)[:-1]]).tolist()
+    send = (np.arange(sum(scounts)) + 1000 * rank).astype(np.float32)
+    recv = np.zeros(sum(rcounts), np.float32)
+    comm.all_to_allv(send, scounts, sdispls, recv, rcounts, rdispls, dt)
+    for p in range(n):
+        pc = [(p + q) % 5 + 1 for q in range(n)]
+        pd = np.concatenate([[0], np.cumsum(pc)[:-1]])
+        exp = (np.arange(pd[rank], pd[rank] + pc[rank]) + 1000 * p).astype(np.float32)
+        assert np.array_equal(recv[rdispls[p]:rdispls[p] + rcounts[p]], exp), "alltoallv"
+    comm.destroy()
+    return worst
+
+
+def rank_that_dies(rank, n, uid, victim):
+    """Failure on the host: one rank exits before the collective; the others must get
+    an error code back (not hang)."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    x = np.ones(1 << 16, np.float32)
+    out = np.empty_like(x)
+    comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)  # connections are up now
+    if rank == victim:
+        os._exit(0)
+    time.sleep(0.3)
+    try:
+        comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+    except capi.FlagcxError as e:
+        return e.code
+    return 0
+
+
+def rank_that_never_joins(rank, n, uid):
+    """Rank n-1 never calls flagcxCommInitRank: the others time out with an error."""
+    if rank == n - 1:
+        return "absent"
+    try:
+        capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    except capi.FlagcxError as e:
+        return e.code
+    return 0
+
+
+def wrong_unique_id(rank, n, uid):
+    bad = bytearray(uid)
+    bad[0] ^= 0xFF  # corrupt the magic
+    try:
+        capi.Comm.init_rank(n, capi.unique_id_from_bytes(bytes(bad)), rank)
+    except capi.FlagcxError as e:
+        return e.code
+    return 0
+
+
+def mismatched_sizes(rank, n, uid):
+    """Ranks disagree on the message size: the receiver sees a size error, not garbage."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    code = 0
+    try:
+        if rank == 0:
+            comm.send(np.ones(1000, np.float32), 1000, capi.FLOAT, 1)
+        elif rank == 1:
+            comm.recv(np.empty(10, np.float32), 10, capi.FLOAT, 0)
+    except capi.FlagcxError as e:
+        code = e.code
+    return code
+
+
+def comm_id_env(rank, n, uid_unused):
+    """Rendezvous through FLAGCX_COMM_ID instead of a shared unique id."""
+    uid = capi.get_unique_id()  # every rank builds the same id from the environment
+    comm = capi.Comm.init_rank(n, uid, rank)
+    x = np.full(8, rank + 1, np.float64)
+    out = np.empty_like(x)
+    comm.all_reduce(x, out, 8, capi.DOUBLE, capi.SUM)
+    comm.destroy()
+    return float(out[0])
+
+
+# ---------------------------------------------------------------------------
+# multi-GPU ranks (one process per GPU)
+# ---------------------------------------------------------------------------
+def _torch_seeded(rank, count, tdt):
+    import torch
+    g = torch.Generator().manual_seed(rank)
+    return (torch.rand(count, generator=g, dtype=torch.float64) * 2 - 1).to(tdt)
+
+
+def gpu_collectives(rank, n, uid, count, registered):
+    """Every device collective on real peers; registered (zero-copy) or staged."""
+    import torch
+    from flagcx_b200.utils.symm import SymmetricBuffer
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    assert comm.device_path, "expected the NVLink device path"
+    worst = {}
+    bufs = []
+
+    def alloc(numel, tdt):
+        if registered:
+            b = SymmetricBuffer(comm, numel * torch.empty((), dtype=tdt).element_size())
+            bufs.append(b)
+            return b.view(tdt, numel)
+        return torch.empty(numel, dtype=tdt, device="cuda")
+
+    for dt, tdt, tol in ((capi.FLOAT, torch.float32, 1e-6), (capi.BFLOAT16, torch.bfloat16, 2 ** -7 * n)):
+        cpu = [_torch_seeded(r, count * n, tdt) for r in range(n)]
+        ref = torch.stack([c.to(torch.float64) for c in cpu]).sum(0)
+        x = alloc(count * n, tdt)
+        x.copy_(cpu[rank])
+        for algo in (capi.ALGO_ONESHOT, capi.ALGO_TWOSHOT):
+            out = alloc(count * n, tdt)
+            comm.all_reduce_fused(x, out, count * n, dt, capi.SUM, algo=algo)
+            torch.cuda.synchronize()
+            err = ((out.cpu().to(torch.float64) - ref).abs() / ref.abs().clamp(min=1)).max().item()
+            worst[f"allreduce{algo}_{dt}"] = err / tol
+        rs = alloc(count, tdt)
+        comm.reduce_scatter(x, rs, count, dt, capi.SUM)
+        torch.cuda.synchronize()
+        err = ((rs.cpu().to(torch.float64) - ref[rank * count:(rank + 1) * count]).abs()
+               / ref[rank * count:(rank + 1) * count].abs().clamp(min=1)).max().item()
+        worst[f"reducescatter_{dt}"] = err / tol
+        for algo in (capi.ALGO_PUSH, capi.ALGO_PULL):
+            ag = alloc(count * n, tdt)
+            ag.zero_()
+            comm.all_gather(x[:count], ag, count, dt, algo=algo)
+            torch.cuda.synchronize()
+            want = torch.cat([c[:count] for c in cpu])
+            worst[f"allgather{algo}_{dt}"] = float(not torch.equal(ag.cpu(), want))
+        aa = alloc(count * n, tdt)
+        comm.all_to_all(x, aa, count, dt)
+        torch.cuda.synchronize()
+        want = torch.cat([cpu[p][rank * count:(rank + 1) * count] for p in range(n)])
+        worst[f"alltoall_{dt}"] = float(not torch.equal(aa.cpu(), want))
+        bc = alloc(count, tdt)
+        bc.copy_(cpu[rank][:count])
+        comm.broadcast(bc, bc, count, dt, n - 1)
+        torch.cuda.synchronize()
+        worst[f"broadcast_{dt}"] = float(not torch.equal(bc.cpu(), cpu[n - 1][:count]))
+    # grouped ring exchange on plain tensors
+    big = (5 << 20) // 4 + 3
+    src = torch.full((big,), float(rank), device="cuda")
+    dst = torch.empty(big, device="cuda")
+    comm.group_start()
+    comm.send(src, big, capi.FLOAT, (rank + 1) % n)
+    comm.recv(dst, big, capi.FLOAT, (rank - 1) % n)
+    comm.group_end()
+    torch.cuda.synchronize()
+    worst["sendrecv"] = float(not bool((dst == float((rank - 1) % n)).all()))
+    comm.barrier()
+    assert comm.async_error() == 0, comm.last_error()
+    for b in bufs:
+        b.free()
+    comm.destroy()
+    return worst
+
+
+def gpu_peer_never_launches(rank, n, uid):
+    """One rank skips the collective: the others' kernels give up after the time limit
+    and report a remote error; nobody hangs and no GPU faults."""
+    import torch
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    comm.set_wait_timeout_ms(300)
+    x = torch.ones(4096, device="cuda")
+    code = 0
+    if rank != n - 1:
+        comm.all_reduce(x, x, x.numel(), capi.FLOAT, capi.SUM)
+        torch.cuda.synchronize()
+        code = comm.async_error()
+        healthy = float((torch.ones(8, device="cuda") * 3).sum()) == 24.0
+        assert healthy
+    # leave between steps, with nothing in flight; abort skips the closing handshake
+    comm.abort()
+    return code

@@ -1,0 +1,111 @@
+"""CPU tier: collectives on host buffers over the TCP bootstrap + socket adaptor,
+checked against numpy, and host-side failure detection.  No GPU needed."""
+import socket
+
+import numpy as np
+import pytest
+
+from flagcx_b200 import capi
+from tests._mp import run_ranks
+
+
+def test_version_and_error_strings():
+    v = capi.C.c_int()
+    capi.check(capi.lib().flagcxGetVersion(capi.C.byref(v)), "flagcxGetVersion")
+    assert v.value == 1300
+    assert b"invalid argument" in capi.lib().flagcxGetErrorString(capi.flagcxInvalidArgument)
+    assert capi.lib().getFlagcxDataTypeSize(capi.BFLOAT16) == 2
+    assert capi.lib().getFlagcxDataTypeSize(capi.DOUBLE) == 8
+
+
+def test_world2_fp32_1mi_elements_matches_numpy():
+    """The headline CPU configuration: world_size=2, fp32, 1,048,576 elements, seed=rank,
+    1e-6 relative error."""
+    res = run_ranks(2, "host_collectives", 1 << 20, capi.FLOAT)
+    for rank, errs in res.items():
+        for name, e in errs.items():
+            assert e <= 1e-6, (rank, name, e)
+
+
+@pytest.mark.parametrize("n", [1, 3, 4])
+def test_other_world_sizes(n):
+    res = run_ranks(n, "host_collectives", 12 * 1024, capi.DOUBLE)
+    for errs in res.values():
+        assert all(e <= 1e-12 for e in errs.values()), errs
+
+
+def test_every_op_dtype_and_reduction():
+    res = run_ranks(3, "host_all_ops", 1237)
+    assert all(w <= 1e-5 for w in res.values()), res
+
+
+def test_multi_socket_striping_and_helper_threads():
+    env = {"FLAGCX_NSOCKS_PERTHREAD": 2, "FLAGCX_SOCKET_NTHREADS": 2, "FLAGCX_SOCKET_STRIPE_MIN": 4096}
+    res = run_ranks(2, "host_collectives", 1 << 18, capi.FLOAT, env=env)
+    for errs in res.values():
+        assert all(e <= 1e-6 for e in errs.values()), errs
+
+
+def test_comm_id_environment_rendezvous():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    res = run_ranks(3, "comm_id_env", env={"FLAGCX_COMM_ID": f"127.0.0.1:{port}"})
+    assert all(v == 6.0 for v in res.values()), res
+
+
+# ---- failure detection on the host ---------------------------------------------------
+def test_dead_rank_gives_an_error_not_a_hang():
+    res = run_ranks(3, "rank_that_dies", 1, env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000}, expect_dead=(1,), timeout=60)
+    assert set(res) == {0, 2}
+    assert all(code in (capi.flagcxRemoteError, capi.flagcxSystemError) for code in res.values()), res
+
+
+def test_absent_rank_times_out_at_init():
+    res = run_ranks(2, "rank_that_never_joins", env={"FLAGCX_SOCKET_TIMEOUT_MS": 1500}, timeout=60)
+    assert res[1] == "absent"
+    assert res[0] in (capi.flagcxRemoteError, capi.flagcxSystemError), res
+
+
+def test_corrupt_unique_id_is_rejected():
+    res = run_ranks(1, "wrong_unique_id")
+    assert res[0] == capi.flagcxInvalidArgument
+
+
+def test_mismatched_message_sizes_are_detected():
+    res = run_ranks(2, "mismatched_sizes", env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000}, timeout=60)
+    assert res[1] in (capi.flagcxInternalError, capi.flagcxRemoteError, capi.flagcxSystemError), res
+
+
+# ---- host reductions (unit level) -------------------------------------------------------
+@pytest.mark.parametrize("op,fn", [(capi.SUM, np.add), (capi.PROD, np.multiply), (capi.MAX, np.maximum),
+                                   (capi.MIN, np.minimum)])
+@pytest.mark.parametrize("dt", [np.int8, np.uint8, np.int32, np.uint32, np.int64, np.uint64, np.float32, np.float64])
+def test_host_reduce_matches_numpy(op, fn, dt):
+    rng = np.random.default_rng(1)
+    a = rng.integers(1, 5, 1001).astype(dt)
+    b = rng.integers(1, 5, 1001).astype(dt)
+    want = fn(a, b)
+    capi.host_reduce(a, b, capi.np_dtype_code(dt), op)
+    assert np.array_equal(a, want)
+
+
+def test_host_reduce_half_and_bfloat16_round_to_nearest_even():
+    rng = np.random.default_rng(2)
+    a = rng.uniform(-4, 4, 4096).astype(np.float16)
+    b = rng.uniform(-4, 4, 4096).astype(np.float16)
+    want = (a.astype(np.float32) + b.astype(np.float32)).astype(np.float16)
+    capi.host_reduce(a, b, capi.HALF, capi.SUM)
+    assert np.array_equal(a, want)
+    # bf16 stored as the upper half of an fp32
+    x = rng.uniform(-4, 4, 4096).astype(np.float32)
+    y = rng.uniform(-4, 4, 4096).astype(np.float32)
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)
+    yb = (y.view(np.uint32) >> 16).astype(np.uint16)
+    xf = (xb.astype(np.uint32) << 16).view(np.float32)
+    yf = (yb.astype(np.uint32) << 16).view(np.float32)
+    s = (xf + yf).view(np.uint32)
+    rounded = ((s + 0x7FFF + ((s >> 16) & 1)) >> 16).astype(np.uint16)
+    capi.host_reduce(xb, yb, capi.BFLOAT16, capi.SUM)
+    assert np.array_equal(xb, rounded)
