@@ -1,0 +1,214 @@
+"""Headline benchmark: training tokens/s of a Llama-3-8B-shaped decoder, bf16,
+fully sharded over N GPUs, one sequence of 4096 tokens per GPU and step
+(weak scaling), synthetic token ids, random-init weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+`value` is measured on the device: CUDA events around K full training steps
+(forward, backward, reduce-scatter, optimizer) on tokens already resident, after W
+warm-up steps, barrier + synchronize on both sides, max over ranks.  `e2e` runs the
+same K steps through the public entry point (flagcx_b200.parallel.fsdp.Trainer.step):
+each step copies its batch from pinned host memory and reads the loss back.
+`--impl reference` runs the unmodified FlagCX torch plugin from baseline/_ref under
+torch FSDP on the same model shape (see baseline/reference_arm.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from flagcx_b200 import ops
+    from flagcx_b200.models.llama import LlamaConfig, build_units
+    from flagcx_b200.parallel.fsdp import ShardedModel, Trainer
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE is {world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        import flagcx_b200.torch_backend as tb
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("flagcx", rank=rank, world_size=world)
+        comm = tb.comm_of(dist.group.WORLD, dev)
+        assert comm.device_path, "expected the NVLink device path"
+
+    cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny()
+    seq = args.seq_len
+    ops.assume_unit_loss_grad = True
+    model = ShardedModel(build_units(cfg), comm, rank, world, dev)
+    trainer = Trainer(model)
+
+    total = args.steps + args.warmup
+    g = torch.Generator().manual_seed(1000 + rank)
+    host_batches = [torch.randint(0, cfg.vocab, (seq + 1,), generator=g, dtype=torch.long).pin_memory()
+                    for _ in range(total)]
+    dev_batches = [b.to(dev) for b in host_batches]
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def max_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up (also through the public entry point) ----
+    losses = []
+    for i in range(args.warmup):
+        losses.append(trainer.step(host_batches[i]))
+    sync_all()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = ops.launch_count + model.comm_launches
+
+    # ---- device-timed region ----
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(args.steps):
+        b = dev_batches[args.warmup + i]
+        loss = model.train_step(b[:-1], b[1:])
+    e1.record()
+    sync_all()
+    dev_ms = max_ranks(e0.elapsed_time(e1))
+    launches = ops.launch_count + model.comm_launches - launches0
+    losses.append(float(loss))
+
+    # ---- end-to-end region: pinned host batch in, loss out, every step ----
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        losses.append(trainer.step(host_batches[args.warmup + i]))
+    torch.cuda.synchronize(dev)
+    e2e_ms = max_ranks((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    tokens = world * seq * args.steps
+    result = {
+        "metric": "training tokens/s (Llama-3-8B shape, FSDP full-shard, bf16)",
+        "value": tokens / (dev_ms / 1e3),
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": dev_ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic uniform-random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {"model": args.model, "params": cfg.num_params(), "global_batch": world, "seq_len": seq,
+                   "parallelism": f"fsdp{world}", "optimizer": "AdamW (bf16 states, fused kernel)",
+                   "l2": "no flush needed: each step streams 16 GB of parameters plus activations, far above the 126 MB L2",
+                   "backend": "flagcx (NVLink kernels of this repository)" if world > 1 else "single GPU, no collectives"},
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": (seq + 1) * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "loss_first_last": [losses[0], losses[-1]],
+    }
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
+    ap.add_argument("--seq-len", type=int, default=4096)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+        out = run_reference(args)
+    else:
+        out = run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

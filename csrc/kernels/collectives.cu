@@ -179,7 +179,34 @@ struct Reducer {
     size_t eb = ub * N, ee = ue * N < elems ? ue * N : elems; // this CTA's elements, relative to sb
     if (vec) {
       const size_t fullEnd = ee / N * N; // whole packs only
-      for (size_t e = eb + (size_t)threadIdx.x * N; e < fullEnd; e += (size_t)blockDim.x * N) {
+      const size_t stride = (size_t)blockDim.x * N;
+      size_t e = eb + (size_t)threadIdx.x * N;
+      if constexpr (NR > 0) {
+        // NVLink loads take microseconds: keep 16 of them in flight per thread
+        constexpr int U = 16 / NR;
+        for (; e + (U - 1) * stride < fullEnd; e += U * stride) {
+          uint4 v[U][NR];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int p = 0; p < NR; ++p) v[u][p] = ldSys16(a.in[p] + (sb + e + u * stride) * sizeof(T));
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            Acc acc[N];
+            const T *e0 = (const T *)&v[u][0];
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] = toAcc<T>(e0[i]);
+#pragma unroll
+            for (int p = 1; p < NR; ++p) {
+              const T *ep = (const T *)&v[u][p];
+#pragma unroll
+              for (int i = 0; i < N; ++i) acc[i] = combine<OP, Acc>(acc[i], toAcc<T>(ep[i]), a.redOp);
+            }
+            storePack(a, dst, nDst, dstBase + e + u * stride, acc);
+          }
+        }
+      }
+      for (; e < fullEnd; e += stride) {
         Acc acc[N];
         loadReduce(a, nRanks, (sb + e) * sizeof(T), acc);
         storePack(a, dst, nDst, dstBase + e, acc);

@@ -129,10 +129,13 @@ __device__ __forceinline__ void ctaCopy(char *dst, const char *src, size_t begin
       const uint4 *s = (const uint4 *)src;
       uint4 *d = (uint4 *)dst;
       size_t i = vb + t;
-      for (; i + 3 * (size_t)n < ve; i += 4 * (size_t)n) {
-        uint4 a0 = ldSys16(s + i), a1 = ldSys16(s + i + n), a2 = ldSys16(s + i + 2 * (size_t)n),
-              a3 = ldSys16(s + i + 3 * (size_t)n);
-        st16(d + i, a0); st16(d + i + n, a1); st16(d + i + 2 * (size_t)n, a2); st16(d + i + 3 * (size_t)n, a3);
+      // peer loads take microseconds: keep eight in flight per thread
+      for (; i + 7 * (size_t)n < ve; i += 8 * (size_t)n) {
+        uint4 r[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) r[u] = ldSys16(s + i + u * (size_t)n);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) st16(d + i + u * (size_t)n, r[u]);
       }
       for (; i < ve; i += n) st16(d + i, ldSys16(s + i));
     }

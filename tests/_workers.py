@@ -291,3 +291,142 @@ def gpu_peer_never_launches(rank, n, uid):
     # leave between steps, with nothing in flight; abort skips the closing handshake
     comm.abort()
     return code
+
+
+# ---------------------------------------------------------------------------
+# torch.distributed backend "flagcx"
+# ---------------------------------------------------------------------------
+def torch_backend_ops(rank, n, uid_unused, port, use_cuda):
+    """Every ProcessGroup operation against values computed by hand."""
+    import torch
+    import torch.distributed as dist
+    import flagcx_b200.torch_backend  # noqa: F401  (registers "flagcx")
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    dist.init_process_group("flagcx", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n)
+    try:
+        t = torch.full((1000,), float(rank + 1), device=dev)
+        dist.all_reduce(t)
+        assert torch.all(t == n * (n + 1) / 2), "allreduce"
+        t = torch.full((1000,), float(rank + 1), device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert torch.all(t == n), "allreduce max"
+        t = torch.full((64,), float(rank), device=dev)
+        dist.broadcast(t, src=n - 1)
+        assert torch.all(t == n - 1), "broadcast"
+        outs = [torch.empty(16, device=dev) for _ in range(n)]
+        dist.all_gather(outs, torch.full((16,), float(rank), device=dev))
+        assert all(torch.all(outs[r] == r) for r in range(n)), "allgather"
+        flat = torch.empty(16 * n, device=dev)
+        dist.all_gather_into_tensor(flat, torch.full((16,), float(rank), device=dev))
+        assert torch.equal(flat, torch.arange(n, device=dev).repeat_interleave(16).float()), "allgather base"
+        rs = torch.empty(8, device=dev)
+        dist.reduce_scatter_tensor(rs, torch.arange(8 * n, device=dev).float())
+        assert torch.equal(rs, torch.arange(8 * rank, 8 * rank + 8, device=dev).float() * n), "reduce_scatter base"
+        rs2 = torch.empty(8, device=dev)
+        dist.reduce_scatter(rs2, [torch.full((8,), float(p), device=dev) for p in range(n)])
+        assert torch.all(rs2 == rank * n), "reduce_scatter list"
+        red = torch.full((32,), 2.0, device=dev)
+        dist.reduce(red, dst=0)
+        if rank == 0:
+            assert torch.all(red == 2.0 * n), "reduce"
+        a2a_in = torch.arange(4 * n, device=dev).float() + 100 * rank
+        a2a_out = torch.empty(4 * n, device=dev)
+        dist.all_to_all_single(a2a_out, a2a_in)
+        want = torch.cat([torch.arange(4 * rank, 4 * rank + 4, device=dev).float() + 100 * p for p in range(n)])
+        assert torch.equal(a2a_out, want), "alltoall base"
+        # uneven splits -> alltoallv
+        in_splits = [(rank + p) % 3 + 1 for p in range(n)]
+        out_splits = [(p + rank) % 3 + 1 for p in range(n)]
+        src = torch.arange(sum(in_splits), device=dev).float() + 1000 * rank
+        dst = torch.empty(sum(out_splits), device=dev)
+        dist.all_to_all_single(dst, src, out_splits, in_splits)
+        off = 0
+        for p in range(n):
+            ps = [(p + q) % 3 + 1 for q in range(n)]
+            start = sum(ps[:rank])
+            want = torch.arange(start, start + ps[rank], device=dev).float() + 1000 * p
+            assert torch.equal(dst[off:off + out_splits[p]], want), "alltoallv"
+            off += out_splits[p]
+        gl = [torch.empty(4, device=dev) for _ in range(n)] if rank == 0 else None
+        dist.gather(torch.full((4,), float(rank), device=dev), gl, dst=0)
+        if rank == 0:
+            assert all(torch.all(gl[r] == r) for r in range(n)), "gather"
+        sc = torch.empty(4, device=dev)
+        dist.scatter(sc, [torch.full((4,), float(p * 3), device=dev) for p in range(n)] if rank == 0 else None, src=0)
+        assert torch.all(sc == rank * 3), "scatter"
+        # p2p ring through batch_isend_irecv (coalesced into one group launch)
+        sendt = torch.full((2048,), float(rank), device=dev)
+        recvt = torch.empty(2048, device=dev)
+        ops = [dist.P2POp(dist.isend, sendt, (rank + 1) % n), dist.P2POp(dist.irecv, recvt, (rank - 1) % n)]
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+        if use_cuda:
+            torch.cuda.synchronize()
+        assert torch.all(recvt == (rank - 1) % n), "batch_isend_irecv"
+        dist.barrier()
+        if use_cuda:
+            torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+    return "ok"
+
+
+def fsdp_losses(rank, n, uid_unused, port, steps):
+    """Tiny Llama through the sharding engine on n GPUs, same batch on every rank."""
+    import torch
+    import torch.distributed as dist
+    from flagcx_b200 import ops
+    from flagcx_b200.models.llama import LlamaConfig, build_units
+    from flagcx_b200.parallel.fsdp import ShardedModel
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    comm = None
+    if n > 1:
+        import flagcx_b200.torch_backend as tb
+        dist.init_process_group("flagcx", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n)
+        comm = tb.comm_of(dist.group.WORLD, dev)
+    cfg = LlamaConfig.tiny()
+    ops.assume_unit_loss_grad = True
+    model = ShardedModel(build_units(cfg), comm, rank, n, dev, lr=1e-3)
+    g = torch.Generator().manual_seed(7)
+    tok = torch.randint(0, cfg.vocab, (257,), generator=g).to(dev)
+    losses = [round(float(model.train_step(tok[:-1], tok[1:])), 4) for _ in range(steps)]
+    if comm is not None:
+        assert comm.async_error() == 0, comm.last_error()
+    model.close()
+    if n > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return losses
+
+
+def torch_ddp_parity(rank, n, uid_unused, port, backend, use_cuda):
+    """A small model under DistributedDataParallel: returns the losses so that the
+    parent can compare backends."""
+    import torch
+    import torch.distributed as dist
+    import flagcx_b200.torch_backend  # noqa: F401
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+    dist.init_process_group(backend, init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 8)).to(dev)
+    ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[rank] if use_cuda else None)
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.05)
+    losses = []
+    g = torch.Generator().manual_seed(100 + rank)
+    for _ in range(5):
+        x = torch.randn(16, 32, generator=g).to(dev)
+        y = torch.randn(16, 8, generator=g).to(dev)
+        loss = torch.nn.functional.mse_loss(ddp(x), y)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        t = loss.detach().clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / n)
+    dist.destroy_process_group()
+    return losses

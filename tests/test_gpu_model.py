@@ -1,0 +1,130 @@
+"""Fused model kernels and the sharding engine against plain PyTorch fp32 references."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests._mp import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from flagcx_b200 import ops
+    ops.ext()  # must be the compiled extension
+    return ops
+
+
+def test_rmsnorm_forward_backward():
+    ops = _ops()
+    torch.manual_seed(0)
+    for H in (256, 4096, 8192):
+        x = torch.randn(37, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_()
+        y = ops.rmsnorm(x, w, 1e-5)
+        g = torch.randn_like(y)
+        y.backward(g)
+        xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+        yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        yr.backward(g.float())
+        assert (y.float() - yr).abs().max() < 0.05
+        assert (x.grad.float() - xf.grad).abs().max() < 0.05
+        assert ((w.grad.float() - wf.grad).abs() / wf.grad.abs().clamp(min=1)).max() < 0.05
+
+
+def test_rope_matches_reference_and_backward_is_inverse():
+    ops = _ops()
+    T, Hn, D = 64, 4, 128
+    x = torch.randn(T, Hn, D, device="cuda", dtype=torch.bfloat16)
+    y = ops.rope(x, 500000.0)
+    half = D // 2
+    inv = 500000.0 ** (-torch.arange(0, half, device="cuda", dtype=torch.float32) * 2 / D)
+    ang = torch.arange(T, device="cuda", dtype=torch.float32)[:, None] * inv[None]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    ref = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+    assert (y.float() - ref).abs().max() < 0.03
+    xg = x.clone().requires_grad_()
+    ops.rope(xg, 500000.0).backward(y)  # rotating back a rotated vector gives the original
+    assert (xg.grad.float() - x.float()).abs().max() < 0.06
+
+
+def test_swiglu_forward_backward():
+    ops = _ops()
+    ab = torch.randn(50, 2 * 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = ops.swiglu(ab)
+    g = torch.randn_like(out)
+    out.backward(g)
+    abf = ab.detach().float().requires_grad_()
+    ref = F.silu(abf[:, :512]) * abf[:, 512:]
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max() < 0.05
+    assert (ab.grad.float() - abf.grad).abs().max() < 0.06
+
+
+def test_cross_entropy_loss_and_gradient():
+    ops = _ops()
+    T, V = 33, 1024
+    logits = (3 * torch.randn(T, V, device="cuda")).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    lf = logits.float().requires_grad_()
+    ref = F.cross_entropy(lf, tgt)
+    ref.backward()
+    work = logits.clone().requires_grad_()
+    w2 = work * 1.0  # non-leaf, as in the model (the kernel overwrites it)
+    loss = ops.cross_entropy_(w2, tgt)
+    loss.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3
+    assert (work.grad.float() - lf.grad).abs().max() < 2e-3
+
+
+def test_adamw_matches_torch():
+    ops = _ops()
+    n = 10007
+    p = torch.randn(n, device="cuda").to(torch.bfloat16)
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    m = torch.zeros_like(p)
+    v = torch.zeros_like(p)
+    pr = torch.nn.Parameter(p.float().clone())
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        pr.grad = g.float()
+        opt.step()
+        ops.adamw_flat_(p, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    assert (p.float() - pr.detach()).abs().max() < 0.03  # bf16 state rounding
+
+
+def test_sharded_engine_world1_matches_fp32_reference():
+    from flagcx_b200 import ops
+    from flagcx_b200.models.llama import LlamaConfig, build_units, reference_forward
+    from flagcx_b200.parallel.fsdp import ShardedModel
+    cfg = LlamaConfig.tiny()
+    ops.assume_unit_loss_grad = True
+    model = ShardedModel(build_units(cfg), None, 0, 1, torch.device("cuda", 0), lr=1e-3)
+    tok = torch.randint(0, cfg.vocab, (129,), device="cuda")
+    params = model.full_parameters()
+    ref = reference_forward(cfg, params, tok[:-1], tok[1:])
+    loss0 = model.train_step(tok[:-1], tok[1:])
+    assert abs(float(loss0) - float(ref)) < 0.05, (float(loss0), float(ref))
+    losses = [float(model.train_step(tok[:-1], tok[1:])) for _ in range(8)]
+    assert losses[-1] < float(loss0) - 0.5, (float(loss0), losses)  # it learns the batch
+    model.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_sharded_engine_world2_matches_world1():
+    """Same seed, same batch on every rank: the sharded run must reproduce the
+    single-GPU losses (gradients are averaged over identical replicas)."""
+    from tests.test_cpu_torch_backend import free_port
+    one = run_ranks(1, "fsdp_losses", free_port(), 4, timeout=300)[0]
+    two = run_ranks(2, "fsdp_losses", free_port(), 4, timeout=300)
+    for a, b in zip(one, two[0]):
+        assert abs(a - b) < 0.05, (one, two[0])
+    assert two[0] == two[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_torch_backend_ops_on_gpus():
+    from tests.test_cpu_torch_backend import free_port
+    n = 2
+    res = run_ranks(n, "torch_backend_ops", free_port(), True, timeout=300)
+    assert all(v == "ok" for v in res.values())
