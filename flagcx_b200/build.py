@@ -33,6 +33,8 @@ def build(verbose: bool = False) -> None:
         ob = None
     if ob is not None:
         ob.build(verbose=verbose)
+    from flagcx_b200.ops import build_noalloc
+    build_noalloc.build(verbose=verbose)
 
 
 if __name__ == "__main__":
