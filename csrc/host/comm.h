@@ -194,5 +194,12 @@ flagcxResult_t emuWorldDestroy(flagcxComm *any);
 // ranks of the world have posted theirs, then launches once.
 flagcxResult_t emuSubmit(flagcxComm *c, int family, const CollArgs *coll, const P2pArgs *p2p, int nCtas,
                          cudaStream_t stream);
+flagcxResult_t emuWindowRegister(flagcxComm *c, void *buff, size_t size, int flags, Window **out);
+// Generic form for kernels with their own argument block.
+constexpr int kMaxEmuBlobBytes = 2048;
+struct LaunchCtx;
+typedef cudaError_t (*EmuBlobLaunch)(const LaunchCtx &lc, const void *deviceArgsArray);
+flagcxResult_t emuSubmitBlob(flagcxComm *c, int kernelId, const void *args, size_t argBytes, int nCtas,
+                             cudaStream_t stream, EmuBlobLaunch launch);
 
 } // namespace fcx

@@ -31,6 +31,10 @@ struct EmuWorld {
   flagcxDevComm *dComms = nullptr;
   CollArgs *dColl = nullptr; // kArgRing * n
   P2pArgs *dP2p = nullptr;   // kArgRing * n
+  // generic kernels (MoE, fused GEMMs): opaque per-rank argument blocks
+  std::vector<std::vector<char>> blob;
+  char *dBlob = nullptr;     // kArgRing * n * kMaxBlobBytes
+  int blobKernel = -1;
   int ring = 0;
   int maxGrid = 0;
 };
@@ -87,6 +91,8 @@ flagcxResult_t emuWorldCreate(int nranks, int dev, flagcxComm **out) {
   FCX_CUDACHECK(cudaMalloc((void **)&w->dComms, sizeof(flagcxDevComm) * nranks));
   FCX_CUDACHECK(cudaMalloc((void **)&w->dColl, sizeof(CollArgs) * nranks * kArgRing));
   FCX_CUDACHECK(cudaMalloc((void **)&w->dP2p, sizeof(P2pArgs) * nranks * kArgRing));
+  FCX_CUDACHECK(cudaMalloc((void **)&w->dBlob, (size_t)kMaxEmuBlobBytes * nranks * kArgRing));
+  w->blob.resize(nranks);
   w->maxGrid = maxCoresidentCtas(FLAGCX_DEVICE_THREADS_PER_CTA);
   FCX_CUDACHECK(cudaDeviceSynchronize());
   for (int r = 0; r < nranks; ++r) out[r] = w->comms[r];
@@ -139,6 +145,7 @@ flagcxResult_t emuWorldDestroy(flagcxComm *any) {
   cudaFree(w->dComms);
   cudaFree(w->dColl);
   cudaFree(w->dP2p);
+  cudaFree(w->dBlob);
   delete w;
   return flagcxSuccess;
 }
@@ -196,6 +203,51 @@ flagcxResult_t emuSubmit(flagcxComm *c, int family, const CollArgs *coll, const 
     e = family == 0 ? launchReduceKernel(lc, w->coll[0], n) : family == 1 ? launchCopyKernel(lc, w->coll[0])
                                                                           : cudaErrorNotSupported;
   }
+  if (e != cudaSuccess) {
+    FCX_WARN("emulated-world launch failed: %s", cudaGetErrorString(e));
+    return flagcxUnhandledDeviceError;
+  }
+  return flagcxSuccess;
+}
+
+// Generic variant for kernels with their own argument block (MoE, fused GEMMs): the
+// blocks are parked per rank; the last arrival copies them to the device and calls
+// `launch(ctx, deviceArray)`, which must do ONE cooperative launch with
+// gridDim.y = ctx.emuRanks.
+flagcxResult_t emuSubmitBlob(flagcxComm *c, int kernelId, const void *args, size_t argBytes, int nCtas,
+                             cudaStream_t stream, EmuBlobLaunch launch) {
+  EmuWorld *w = c->emu;
+  const int n = w->n, r = c->rank;
+  if (argBytes > (size_t)kMaxEmuBlobBytes) return flagcxInternalError;
+  if (w->has[r]) {
+    FCX_WARN("emulated rank %d posted a second operation before the others posted their first", r);
+    return flagcxInvalidUsage;
+  }
+  if (w->posted == 0) { w->blobKernel = kernelId; w->nCtas = nCtas; }
+  if (kernelId != w->blobKernel) {
+    FCX_WARN("emulated ranks posted different kinds of operations");
+    return flagcxInvalidUsage;
+  }
+  w->nCtas = std::min(w->nCtas, nCtas);
+  w->blob[r].assign((const char *)args, (const char *)args + argBytes);
+  w->has[r] = 1;
+  if (++w->posted < n) return flagcxSuccess;
+  w->posted = 0;
+  std::fill(w->has.begin(), w->has.end(), 0);
+  const int slot = w->ring++ % kArgRing;
+  std::vector<flagcxDevComm> devs(n);
+  for (int q = 0; q < n; ++q) devs[q] = w->comms[q]->dev;
+  FCX_CUDACHECK(cudaMemcpyAsync(w->dComms, devs.data(), sizeof(flagcxDevComm) * n, cudaMemcpyHostToDevice, stream));
+  char *d = w->dBlob + (size_t)slot * n * kMaxEmuBlobBytes;
+  std::vector<char> packed((size_t)n * argBytes);
+  for (int q = 0; q < n; ++q) memcpy(packed.data() + (size_t)q * argBytes, w->blob[q].data(), argBytes);
+  FCX_CUDACHECK(cudaMemcpyAsync(d, packed.data(), packed.size(), cudaMemcpyHostToDevice, stream));
+  LaunchCtx lc;
+  lc.stream = stream;
+  lc.emuRanks = n;
+  lc.emuComms = w->dComms;
+  lc.nCtas = std::max(1, std::min(w->nCtas, std::max(1, w->maxGrid / n)));
+  cudaError_t e = launch(lc, d);
   if (e != cudaSuccess) {
     FCX_WARN("emulated-world launch failed: %s", cudaGetErrorString(e));
     return flagcxUnhandledDeviceError;

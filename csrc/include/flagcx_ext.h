@@ -89,6 +89,27 @@ flagcxResult_t flagcxWindowGetMulticastPointer(flagcxWindow_t win, size_t offset
 flagcxResult_t flagcxEmuWorldCreate(int nranks, int device, flagcxComm_t *comms);
 flagcxResult_t flagcxEmuWorldDestroy(flagcxComm_t anyRank);
 
+/* ---- expert-parallel (MoE) dispatch / combine ------------------------------------------
+ * Create is collective: it allocates, on every rank, a peer-mapped receive buffer and an
+ * expert-output buffer of capacityRows x hidden bf16 each.  Experts are spread evenly:
+ * rank r owns experts [r*E/n, (r+1)*E/n).
+ *
+ * Dispatch copies every (token, chosen expert) row to the owning rank, grouped by
+ * expert; afterwards the rows of local expert e are recvRows[offsets[e] .. offsets[e+1]).
+ * The caller runs its experts over those rows and writes the results to the same rows of
+ * expertOutRows.  Combine then produces out[t] = sum_k weights[t,k] * expertOut(t,k).
+ * A dispatch whose rows exceed capacityRows on some rank is reported through
+ * flagcxCommGetAsyncError (flagcxInvalidArgument); nothing is written out of bounds. */
+typedef struct flagcxMoe *flagcxMoe_t;
+flagcxResult_t flagcxMoeCreate(flagcxComm_t comm, int maxTokens, int hidden, int topk, int nExperts,
+                               size_t capacityRows, flagcxMoe_t *moe);
+flagcxResult_t flagcxMoeDestroy(flagcxMoe_t moe);
+flagcxResult_t flagcxMoeGetBuffers(flagcxMoe_t moe, void **recvRows, void **expertOutRows, int **expertOffsets);
+flagcxResult_t flagcxMoeDispatch(flagcxMoe_t moe, const void *x, const int *topkIdx, int nTokens,
+                                 flagcxStream_t stream);
+flagcxResult_t flagcxMoeCombine(flagcxMoe_t moe, const float *topkWeights, void *out, int nTokens,
+                                flagcxStream_t stream);
+
 /* Host-side element-wise reduction used by the socket path (exposed for tests). */
 flagcxResult_t flagcxHostReduce(void *dst, const void *src, size_t count, flagcxDataType_t dtype,
                                 flagcxRedOp_t op);

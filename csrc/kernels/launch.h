@@ -17,7 +17,14 @@ struct LaunchCtx {
   const flagcxDevComm *emuComms = nullptr;
   const CollArgs *emuArgs = nullptr;
   const P2pArgs *emuP2p = nullptr;
+  const void *emuBlob = nullptr; // per-rank argument blocks of the other kernel families
 };
+
+struct MoeArgs;
+cudaError_t launchMoeCount(cudaStream_t s, const int *topkIdx, int *counts, int *pos, int items, int nExperts,
+                           flagcxDevStatus *status);
+cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a);
+cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a);
 
 cudaError_t launchReduceKernel(const LaunchCtx &lc, const CollArgs &a, int nRanks);
 cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a);

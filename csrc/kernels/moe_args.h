@@ -1,0 +1,28 @@
+// moe_args.h -- argument block of the MoE dispatch / combine kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <stddef.h>
+
+#include "flagcx_device.cuh"
+
+#define FLAGCX_MOE_MAX_TOPK 8
+#define FLAGCX_MOE_MAX_EXPERTS 1024
+
+namespace fcx {
+
+struct MoeArgs {
+  const __nv_bfloat16 *x;  // [T, H] local activations (dispatch input)
+  const int *topkIdx;      // [T, K] global expert ids
+  const float *topkW;      // [T, K] gate weights (combine)
+  __nv_bfloat16 *out;      // [T, H] combine output
+  int *countsAll[FLAGCX_MAX_RANKS]; // countsAll[p]: rank p's table [nRanks][E]; row r = counts of rank r
+  int *pos;                // [T*K] index of the pair within its (source rank, expert) group
+  int *route;              // [T*K][2] destination rank and row of each pair
+  char *recv[FLAGCX_MAX_RANKS];      // recv[p]: rank p's receive buffer [capacity, H] bf16
+  char *expertOut[FLAGCX_MAX_RANKS]; // expertOut[p]: rank p's expert outputs, same row order
+  int *expertOffsets;      // local [EPR + 1]: row range of each local expert
+  int T, H, K, E, EPR;
+  size_t capacity;         // rows in recv / expertOut
+};
+
+} // namespace fcx
