@@ -38,6 +38,7 @@ struct Driver {
   FCX_DRV(cuMulticastGetGranularity)
   FCX_DRV(cuStreamWriteValue64)
   FCX_DRV(cuStreamWaitValue64)
+  FCX_DRV(cuTensorMapEncodeTiled)
 #undef FCX_DRV
 };
 
@@ -84,6 +85,7 @@ Driver *driver() {
     FCX_LOAD(cuMulticastGetGranularity, false)
     FCX_LOAD(cuStreamWriteValue64, true)
     FCX_LOAD(cuStreamWaitValue64, true)
+    FCX_LOAD(cuTensorMapEncodeTiled, false)
 #undef FCX_LOAD
     d.ok = all;
   });
@@ -345,6 +347,20 @@ flagcxResult_t addressRange(const void *p, void **base, size_t *size) {
   FCX_CUCHECK(d->p_cuMemGetAddressRange(&b, &s, (CUdeviceptr)p));
   *base = (void *)b;
   *size = s;
+  return flagcxSuccess;
+}
+
+flagcxResult_t tensorMap2dBf16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint32_t boxRows,
+                               uint32_t boxCols) {
+  Driver *d = driver();
+  if (!d->p_cuTensorMapEncodeTiled) return flagcxNotSupported;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {boxCols, boxRows};
+  cuuint32_t estr[2] = {1, 1};
+  FCX_CUCHECK(d->p_cuTensorMapEncodeTiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
+                                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   return flagcxSuccess;
 }
 

@@ -87,6 +87,12 @@ PtrKind classify(const void *p, int *dev);
 // Base and size of the driver allocation containing p.
 flagcxResult_t addressRange(const void *p, void **base, size_t *size);
 
+// Tensor map for TMA tile loads of a row-major bf16 matrix [rows, cols] (cols
+// contiguous), box of boxRows x boxCols elements, 128-byte swizzle.  boxCols * 2 must
+// be 128; base 16-byte aligned; cols * 2 a multiple of 16.
+flagcxResult_t tensorMap2dBf16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint32_t boxRows,
+                               uint32_t boxCols);
+
 // Stream-ordered 64-bit write / wait on device memory.
 flagcxResult_t streamWriteValue64(cudaStream_t s, void *addr, uint64_t v);
 flagcxResult_t streamWaitValueGeq64(cudaStream_t s, void *addr, uint64_t v);

@@ -110,6 +110,28 @@ flagcxResult_t flagcxMoeDispatch(flagcxMoe_t moe, const void *x, const int *topk
 flagcxResult_t flagcxMoeCombine(flagcxMoe_t moe, const float *topkWeights, void *out, int nTokens,
                                 flagcxStream_t stream);
 
+/* ---- tensor-core GEMM and fused tensor-parallel layers ---------------------------------
+ * All matrices are bf16, row-major with K contiguous: D[M,N] = A[M,K] * B[N,K]^T, fp32
+ * accumulation on the tcgen05 tensor cores.  M %% 128 == 0, N %% 256 == 0, K %% 64 == 0. */
+flagcxResult_t flagcxGemmBf16(const void *A, const void *B, void *D, int M, int N, int K, flagcxStream_t stream);
+
+/* mode 1, all-gather -> GEMM (column-parallel): the activation matrix [M,K] is split by
+ * rows over the ranks.  Each rank writes its [M/n, K] shard at the address returned by
+ * flagcxTpGemmGetShard and calls flagcxTpAllGatherGemm with its weight slice B[N,K]; one
+ * kernel moves the shards between the ranks and computes D[M,N], starting with the local
+ * rows and taking up remote rows as they arrive.
+ * mode 2, GEMM -> reduce-scatter (row-parallel): each rank holds A[M,K] and B[N,K] for its
+ * slice of K; one kernel computes the partial products, delivers every tile to the rank
+ * that owns its rows and sums the partials there: out[M/n, N].
+ * Create/Destroy are collective. */
+typedef struct flagcxTpGemm *flagcxTpGemm_t;
+flagcxResult_t flagcxTpGemmCreate(flagcxComm_t comm, int mode, int M, int N, int K, flagcxTpGemm_t *handle);
+flagcxResult_t flagcxTpGemmDestroy(flagcxTpGemm_t handle);
+flagcxResult_t flagcxTpGemmGetShard(flagcxTpGemm_t handle, void **localShard);
+flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t handle, const void *B, void *D, flagcxStream_t stream);
+flagcxResult_t flagcxTpGemmReduceScatter(flagcxTpGemm_t handle, const void *A, const void *B, void *out,
+                                         flagcxStream_t stream);
+
 /* Host-side element-wise reduction used by the socket path (exposed for tests). */
 flagcxResult_t flagcxHostReduce(void *dst, const void *src, size_t count, flagcxDataType_t dtype,
                                 flagcxRedOp_t op);

@@ -1,0 +1,27 @@
+// tp_gemm_args.h -- argument block of the tcgen05 GEMM / fused tensor-parallel kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <stddef.h>
+
+#include "flagcx_device.cuh"
+
+namespace fcx {
+
+enum TpGemmMode : int { kPlain = 0, kAllGatherGemm = 1, kGemmReduceScatter = 2 };
+
+struct TpGemmArgs {
+  __nv_bfloat16 *D; // [M, N] output (plain, all-gather modes)
+  int M, N, K, mode;
+  int rowsPerRank;  // M / nRanks
+  int nPushCtas;    // CTAs that push the local shard (all-gather mode)
+  unsigned long long epoch; // call counter of this handle, starts at 1
+  // all-gather -> GEMM
+  __nv_bfloat16 *gathered[FLAGCX_MAX_RANKS];      // rank p's gather buffer [M, K] as mapped here
+  unsigned long long *chunkFlags[FLAGCX_MAX_RANKS]; // rank p's flags [nRanks][rowsPerRank/128]
+  // GEMM -> reduce-scatter
+  __nv_bfloat16 *partial[FLAGCX_MAX_RANKS];       // rank p's partial buffer [nRanks][rowsPerRank, N]
+  unsigned long long *rowFlags[FLAGCX_MAX_RANKS];   // rank p's counters [rowsPerRank/128]
+  __nv_bfloat16 *out;                              // [rowsPerRank, N] reduced rows of this rank
+};
+
+} // namespace fcx

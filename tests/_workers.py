@@ -373,6 +373,47 @@ def torch_backend_ops(rank, n, uid_unused, port, use_cuda):
     return "ok"
 
 
+def tp_fused(rank, n, uid, M, N, K):
+    """all-gather->GEMM and GEMM->reduce-scatter against torch on gathered operands."""
+    import torch
+    from flagcx_b200.parallel.tp import AllGatherGemm, GemmReduceScatter
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    rows = M // n
+
+    def seeded(seed, shape):
+        g = torch.Generator().manual_seed(seed)
+        return (torch.randn(*shape, generator=g) * 0.5).to(torch.bfloat16)
+
+    out = {}
+    # column-parallel: X sharded by rows, every rank its own W
+    xs = [seeded(10 + r, (rows, K)) for r in range(n)]
+    w = seeded(100 + rank, (N, K)).cuda()
+    agg = AllGatherGemm(comm, M, N, K)
+    for it in range(3):  # several calls: flags are epochs, buffers are reused
+        agg.shard.copy_(xs[rank].cuda() * (it + 1))
+        d = agg(w)
+        torch.cuda.synchronize()
+        ref = (torch.cat(xs).float().cuda() * (it + 1)) @ w.float().T
+        err = ((d.float() - ref).abs() / (ref.abs().mean() + ref.abs())).max().item()
+        out["ag_gemm"] = max(out.get("ag_gemm", 0.0), err)
+    agg.close()
+    # row-parallel: every rank a K-slice; the sum over ranks is scattered by rows
+    xk = [seeded(200 + r, (M, K)) for r in range(n)]
+    wk = [seeded(300 + r, (N, K)) for r in range(n)]
+    grs = GemmReduceScatter(comm, M, N, K)
+    for it in range(3):
+        o = grs(xk[rank].cuda(), wk[rank].cuda())
+        torch.cuda.synchronize()
+        ref = sum((xk[r].float() @ wk[r].float().T) for r in range(n))[rank * rows:(rank + 1) * rows].cuda()
+        err = ((o.float() - ref).abs() / (ref.abs().mean() + ref.abs())).max().item()
+        out["gemm_rs"] = max(out.get("gemm_rs", 0.0), err)
+    grs.close()
+    assert comm.async_error() == 0, comm.last_error()
+    comm.destroy()
+    return out
+
+
 def fsdp_losses(rank, n, uid_unused, port, steps):
     """Tiny Llama through the sharding engine on n GPUs, same batch on every rank."""
     import torch
