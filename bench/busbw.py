@@ -73,6 +73,15 @@ def main():
     args = ap.parse_args()
 
     w = init_world()
+
+    def _abort_on_error(tp, val, tb):
+        # leave no memory bound to a multicast object behind when this rank dies of an error
+        try:
+            w.comm.abort()
+        finally:
+            sys.__excepthook__(tp, val, tb)
+
+    sys.excepthook = _abort_on_error
     n, rank = w.world, w.rank
     lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
     flush = None if args.no_flush else torch.zeros(64 << 20, dtype=torch.float32, device="cuda")

@@ -443,6 +443,41 @@ def fsdp_losses(rank, n, uid_unused, port, steps):
     return losses
 
 
+def torch_fsdp2_losses(rank, n, uid_unused, port, backend):
+    """torch's own FSDP (fully_shard) on GPUs over the given backend: per-step losses."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+    import flagcx_b200.torch_backend  # noqa: F401
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group(backend, init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n)
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(256, 512, bias=False), nn.GELU(), nn.Linear(512, 512, bias=False), nn.GELU(),
+                          nn.Linear(512, 64, bias=False)).to(dev).to(torch.bfloat16)
+    for layer in model:
+        if isinstance(layer, nn.Linear):
+            fully_shard(layer)
+    fully_shard(model)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(50 + rank)
+    losses = []
+    for _ in range(5):
+        x = torch.randn(32, 256, generator=g).to(dev).to(torch.bfloat16)
+        y = torch.randn(32, 64, generator=g).to(dev).to(torch.bfloat16)
+        loss = (model(x).float() - y.float()).pow(2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        t = loss.detach().clone()
+        dist.all_reduce(t)
+        losses.append(round(float(t) / n, 4))
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+    return losses
+
+
 def torch_ddp_parity(rank, n, uid_unused, port, backend, use_cuda):
     """A small model under DistributedDataParallel: returns the losses so that the
     parent can compare backends."""

@@ -123,6 +123,16 @@ def test_sharded_engine_world2_matches_world1():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_torch_fsdp_over_flagcx_matches_nccl():
+    """torch.distributed.fsdp.fully_shard with backend='flagcx' trains like backend='nccl'."""
+    from tests.test_cpu_torch_backend import free_port
+    ours = run_ranks(2, "torch_fsdp2_losses", free_port(), "flagcx", timeout=300)
+    nccl = run_ranks(2, "torch_fsdp2_losses", free_port(), "nccl", timeout=300)
+    for a, b in zip(ours[0], nccl[0]):
+        assert abs(a - b) <= 0.02 * max(1.0, abs(b)), (ours[0], nccl[0])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_torch_backend_ops_on_gpus():
     from tests.test_cpu_torch_backend import free_port
     n = 2
