@@ -49,13 +49,14 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
     case flagcxCommOpAllReduce: {
       size_t oneShotMax = paramOneShotMaxBytes() > 0 ? (size_t)paramOneShotMaxBytes()
                           : nranks <= 2 ? (8u << 20) : nranks <= 4 ? (512u << 10) : (256u << 10);
-      if (nvlsOk) ch.algo = bytes < (1u << 20) ? FLAGCX_ALGO_NVLS_ONESHOT : FLAGCX_ALGO_NVLS_TWOSHOT;
+      // with two ranks the switch saves no traffic over a plain peer read
+      if (nvlsOk && nranks > 2) ch.algo = bytes < (1u << 20) ? FLAGCX_ALGO_NVLS_ONESHOT : FLAGCX_ALGO_NVLS_TWOSHOT;
       else ch.algo = bytes <= oneShotMax ? FLAGCX_ALGO_ONESHOT : FLAGCX_ALGO_TWOSHOT;
       if (ch.algo == FLAGCX_ALGO_TWOSHOT || ch.algo == FLAGCX_ALGO_NVLS_TWOSHOT) work = bytes / std::max(1, nranks);
       break;
     }
     case flagcxCommOpReduceScatter:
-      ch.algo = nvlsOk && bytes >= (1u << 20) ? FLAGCX_ALGO_NVLS : FLAGCX_ALGO_PULL;
+      ch.algo = nvlsOk && nranks > 2 && bytes >= (1u << 20) ? FLAGCX_ALGO_NVLS : FLAGCX_ALGO_PULL;
       work = bytes / std::max(1, nranks);
       break;
     case flagcxCommOpAllGather:

@@ -545,6 +545,35 @@ __device__ __forceinline__ uint4 scalePack(uint4 v, float scale) {
   return v;
 }
 
+// Streams packs [ub, ue) from src (+srcBase packs) to dst (+dstBase packs), eight loads in
+// flight per thread: through the switch (multimem.ld_reduce / multimem.st) or plainly.
+template <typename T, bool MC_LOAD, bool MC_STORE>
+__device__ __forceinline__ void nvlsStream(const char *src, char *dst, size_t ub, size_t ue, size_t srcBase,
+                                           size_t dstBase, int redOp, float scale, int t, int nt) {
+  constexpr int U = 8;
+  size_t i = ub + t;
+  for (; i + (U - 1) * (size_t)nt < ue; i += U * (size_t)nt) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const char *p = src + ((srcBase + i + u * (size_t)nt) << 4);
+      v[u] = MC_LOAD ? Mm<T>::ldReduce(p, redOp) : ldSys16(p);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      char *q = dst + ((dstBase + i + u * (size_t)nt) << 4);
+      uint4 o = scalePack<T>(v[u], scale);
+      if (MC_STORE) Mm<T>::st(q, o); else st16(q, o);
+    }
+  }
+  for (; i < ue; i += nt) {
+    const char *p = src + ((srcBase + i) << 4);
+    uint4 o = scalePack<T>(MC_LOAD ? Mm<T>::ldReduce(p, redOp) : ldSys16(p), scale);
+    char *q = dst + ((dstBase + i) << 4);
+    if (MC_STORE) Mm<T>::st(q, o); else st16(q, o);
+  }
+}
+
 // All sizes here are whole 16-byte packs (the host falls back otherwise).
 template <typename T>
 __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) nvlsKernel(const flagcxDevComm c, const CollArgs a) {
@@ -558,10 +587,7 @@ __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) nvlsKernel(cons
   switch (a.kind) {
     case kAllReduceNvlsOneShot: {
       ctaShare(a.count / N, b, g, &ub, &ue);
-      for (size_t i = ub + t; i < ue; i += nt) {
-        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp), a.scale);
-        st16(a.out[rank] + (i << 4), v);
-      }
+      nvlsStream<T, true, false>(a.mcIn, a.out[rank], ub, ue, 0, 0, a.redOp, a.scale, t, nt);
       break;
     }
     case kAllReduceNvlsTwoShot: {
@@ -570,35 +596,17 @@ __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) nvlsKernel(cons
       size_t se = sb + s < a.count ? sb + s : a.count;
       ctaShare((se - sb) / N, b, g, &ub, &ue);
       size_t base = sb / N;
-      size_t i = base + ub + t;
-      for (; i + nt < base + ue; i += 2 * (size_t)nt) {
-        uint4 v0 = Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp);
-        uint4 v1 = Mm<T>::ldReduce(a.mcIn + ((i + nt) << 4), a.redOp);
-        Mm<T>::st(a.mcOut + (i << 4), scalePack<T>(v0, a.scale));
-        Mm<T>::st(a.mcOut + ((i + nt) << 4), scalePack<T>(v1, a.scale));
-      }
-      for (; i < base + ue; i += nt) {
-        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + (i << 4), a.redOp), a.scale);
-        Mm<T>::st(a.mcOut + (i << 4), v);
-      }
+      nvlsStream<T, true, true>(a.mcIn, a.mcOut, ub, ue, base, base, a.redOp, a.scale, t, nt);
       break;
     }
     case kReduceScatterNvls: {
       ctaShare(a.count / N, b, g, &ub, &ue);
-      size_t base = a.inStride * rank >> 4;
-      for (size_t i = ub + t; i < ue; i += nt) {
-        uint4 v = scalePack<T>(Mm<T>::ldReduce(a.mcIn + ((base + i) << 4), a.redOp), a.scale);
-        st16(a.out[rank] + (i << 4), v);
-      }
+      nvlsStream<T, true, false>(a.mcIn, a.out[rank], ub, ue, a.inStride * rank >> 4, 0, a.redOp, a.scale, t, nt);
       break;
     }
     case kAllGatherNvls: {
       ctaShare(a.count / N, b, g, &ub, &ue);
-      size_t base = a.outStride * rank >> 4;
-      for (size_t i = ub + t; i < ue; i += nt) {
-        uint4 v = ldSys16(a.in[rank] + (i << 4));
-        Mm<T>::st(a.mcOut + ((base + i) << 4), v);
-      }
+      nvlsStream<T, false, true>(a.in[rank], a.mcOut, ub, ue, 0, a.outStride * rank >> 4, a.redOp, 1.0f, t, nt);
       break;
     }
     default: break;
