@@ -10,9 +10,9 @@
 #include "flagcx_ext.h"
 
 namespace fcx {
-size_t tpGemmSmemBytes();
+size_t tpGemmSmemBytes(bool pair);
 cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const flagcxDevComm &c,
-                         const TpGemmArgs &a, int nCtas);
+                         const TpGemmArgs &a, int nCtas, bool pair);
 } // namespace fcx
 
 using namespace fcx;
@@ -29,6 +29,9 @@ struct flagcxTpGemm {
 };
 
 namespace {
+
+// CTA pairs (256-row tiles, cta_group::2) whenever the row blocks allow it.
+bool usePair(int rowsPerOwner) { return readParam("GEMM_PAIR", 1) != 0 && rowsPerOwner % 256 == 0; }
 
 int smCount() {
   int dev = 0, sms = 0;
@@ -89,7 +92,8 @@ flagcxResult_t flagcxGemmBf16(const void *A, const void *B, void *D, int M, int 
   FCXCHECK(checkShape(M, N, K));
   CUtensorMap ta, tb;
   FCXCHECK(cu::tensorMap2dBf16(&ta, A, M, K, 128, 64));
-  FCXCHECK(cu::tensorMap2dBf16(&tb, B, N, K, 256, 64));
+  const bool pair = usePair(M);
+  FCXCHECK(cu::tensorMap2dBf16(&tb, B, N, K, pair ? 128 : 256, 64));
   flagcxDevComm c;
   memset(&c, 0, sizeof c);
   c.nRanks = 1;
@@ -101,7 +105,8 @@ flagcxResult_t flagcxGemmBf16(const void *A, const void *B, void *D, int M, int 
   a.mode = kPlain;
   a.rowsPerRank = M;
   int tiles = (M / 128) * (N / 256);
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, ta, tb, c, a, std::min(tiles, smCount()));
+  if (pair) tiles = 2 * ((M / 256) * (N / 256));
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, ta, tb, c, a, std::min(tiles, smCount()), pair);
   if (e != cudaSuccess) { FCX_WARN("GEMM launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }
@@ -154,7 +159,8 @@ flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t h, const void *B, void *D, f
   flagcxComm *c = h->comm;
   if (c->asyncError.load() != flagcxSuccess) return (flagcxResult_t)c->asyncError.load();
   const CUtensorMap *tb;
-  FCXCHECK(cachedMap(h->mapsB, B, h->N, h->K, 256, &tb));
+  const bool pair = usePair(h->rowsPerRank);
+  FCXCHECK(cachedMap(h->mapsB, B, h->N, h->K, pair ? 128 : 256, &tb));
   TpGemmArgs a;
   memset(&a, 0, sizeof a);
   a.D = (__nv_bfloat16 *)D;
@@ -167,8 +173,11 @@ flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t h, const void *B, void *D, f
     a.chunkFlags[p] = (unsigned long long *)h->wFlags->peer[p];
   }
   const int sms = smCount();
-  a.nPushCtas = c->nranks > 1 ? (int)std::max<int64_t>(1, std::min<int64_t>(readParam("TP_PUSH_CTAS", 16), sms / 2)) : 0;
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, h->tmGather, *tb, c->dev, a, sms);
+  // a chunk is 128 rows = (K/64) x 16 KiB; pieces of at most 64 KiB that divide it evenly
+  int units = h->K / 64, per = 4;
+  while (units % per) --per;
+  a.piecesPerChunk = units / per;
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, h->tmGather, *tb, c->dev, a, sms, pair);
   if (e != cudaSuccess) { FCX_WARN("all-gather GEMM launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }
@@ -179,8 +188,9 @@ flagcxResult_t flagcxTpGemmReduceScatter(flagcxTpGemm_t h, const void *A, const 
   flagcxComm *c = h->comm;
   if (c->asyncError.load() != flagcxSuccess) return (flagcxResult_t)c->asyncError.load();
   const CUtensorMap *ta, *tb;
+  const bool pair = usePair(h->rowsPerRank);
   FCXCHECK(cachedMap(h->mapsA, A, h->M, h->K, 128, &ta));
-  FCXCHECK(cachedMap(h->mapsB, B, h->N, h->K, 256, &tb));
+  FCXCHECK(cachedMap(h->mapsB, B, h->N, h->K, pair ? 128 : 256, &tb));
   TpGemmArgs a;
   memset(&a, 0, sizeof a);
   a.M = h->M; a.N = h->N; a.K = h->K;
@@ -192,7 +202,7 @@ flagcxResult_t flagcxTpGemmReduceScatter(flagcxTpGemm_t h, const void *A, const 
     a.partial[p] = (__nv_bfloat16 *)h->wBuf->peer[p];
     a.rowFlags[p] = (unsigned long long *)h->wFlags->peer[p];
   }
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, *ta, *tb, c->dev, a, smCount());
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, *ta, *tb, c->dev, a, smCount(), pair);
   if (e != cudaSuccess) { FCX_WARN("GEMM reduce-scatter launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }

@@ -70,7 +70,9 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
   }
   (void)registered;
   size_t perCta = 16u << 10;
-  ch.nCtas = (int)std::max<size_t>(1, std::min<size_t>((work + perCta - 1) / perCta, (size_t)maxCtas));
+  // bandwidth-bound sizes get twice the CTAs: more NVLink accesses in flight
+  size_t cap = work >= (16u << 20) ? std::min<size_t>(2 * (size_t)maxCtas, FLAGCX_COLL_BARRIER_SLOTS) : (size_t)maxCtas;
+  ch.nCtas = (int)std::max<size_t>(1, std::min<size_t>((work + perCta - 1) / perCta, cap));
   return ch;
 }
 

@@ -379,17 +379,53 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
       ctaCopyShare(a.out[rank], a.in[a.root] + a.inStride * rank, blk, b, g);
       break;
     case kAllToAllPush:
+    case kAllToAllPull: {
+      // one block per peer; all peers' blocks advance together so that every link is
+      // busy at once and each thread keeps one access per peer in flight
+      const char *src[FLAGCX_MAX_RANKS];
+      char *dst[FLAGCX_MAX_RANKS];
+      bool vec = true;
       for (int k = 0; k < n; ++k) {
         int p = rank + k; if (p >= n) p -= n;
-        ctaCopyShare(a.out[p] + a.outStride * rank, a.in[rank] + a.inStride * p, blk, b, g);
+        if (a.kind == kAllToAllPush) {
+          src[k] = a.in[rank] + a.inStride * p;
+          dst[k] = a.out[p] + a.outStride * rank;
+        } else {
+          src[k] = a.in[p] + a.inStride * rank;
+          dst[k] = a.out[rank] + a.outStride * p;
+        }
+        vec &= ((((uintptr_t)src[k]) | ((uintptr_t)dst[k])) & 15) == 0;
       }
-      break;
-    case kAllToAllPull:
-      for (int k = 0; k < n; ++k) {
-        int p = rank + k; if (p >= n) p -= n;
-        ctaCopyShare(a.out[rank] + a.outStride * p, a.in[p] + a.inStride * rank, blk, b, g);
+      if (!vec) {
+        for (int k = 0; k < n; ++k) ctaCopyShare(dst[k], src[k], blk, b, g);
+        break;
       }
+      size_t ub, ue;
+      ctaShare((blk + 15) >> 4, b, g, &ub, &ue);
+      const size_t ve = blk >> 4 < ue ? blk >> 4 : ue; // whole 16-byte packs of this CTA's share
+      const int t = threadIdx.x, nt = blockDim.x;
+      size_t i = ub + t;
+      for (; i + nt < ve; i += 2 * (size_t)nt) {
+        uint4 v0[FLAGCX_MAX_RANKS], v1[FLAGCX_MAX_RANKS];
+#pragma unroll
+        for (int k = 0; k < FLAGCX_MAX_RANKS; ++k)
+          if (k < n) { v0[k] = ldSys16(src[k] + (i << 4)); v1[k] = ldSys16(src[k] + ((i + nt) << 4)); }
+#pragma unroll
+        for (int k = 0; k < FLAGCX_MAX_RANKS; ++k)
+          if (k < n) { st16(dst[k] + (i << 4), v0[k]); st16(dst[k] + ((i + nt) << 4), v1[k]); }
+      }
+      for (; i < ve; i += nt) {
+#pragma unroll
+        for (int k = 0; k < FLAGCX_MAX_RANKS; ++k)
+          if (k < n) st16(dst[k] + (i << 4), ldSys16(src[k] + (i << 4)));
+      }
+      // bytes past the last whole pack of the block (the last CTA share only)
+      const size_t tailBegin = (blk >> 4) << 4;
+      if (ub < ue && ue * 16 >= blk && tailBegin < blk)
+        for (int k = 0; k < n; ++k)
+          for (size_t j = tailBegin + t; j < blk; j += nt) dst[k][j] = src[k][j];
       break;
+    }
     case kAllToAllvPull:
       for (int k = 0; k < n; ++k) {
         int p = rank + k; if (p >= n) p -= n;

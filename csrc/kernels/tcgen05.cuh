@@ -130,5 +130,62 @@ __device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one 256-row MMA -----------
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapToCta(uint32_t localSmemAddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(localSmemAddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// Tile load into THIS CTA's shared memory whose bytes are counted on an mbarrier that may
+// live in the partner CTA (given as a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tmaLoad2dPair(void *smemDst, const CUtensorMap *map, int c0, int c1,
+                                              uint32_t barClusterAddr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smemAddr(smemDst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(barClusterAddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmemAllocPair(uint32_t *smemResult, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(smemResult)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmemRelinquishPair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemDeallocPair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D (128 rows in each CTA's TMEM) (+)= A (128 rows from each CTA) * B^T (N/2 rows from each CTA)
+__device__ __forceinline__ void mmaBf16Pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc,
+                                            bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmemD),
+      "l"(descA), "l"(descB), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+// One arrival on the mbarrier at the same offset in every CTA named by ctaMask.
+__device__ __forceinline__ void mmaCommitPair(uint64_t *bar, uint16_t ctaMask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smemAddr(bar)),
+      "h"(ctaMask)
+      : "memory");
+}
+
 } // namespace tc
 } // namespace fcx

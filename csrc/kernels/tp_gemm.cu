@@ -4,23 +4,33 @@
 //
 //   mode kPlain           D[M,N] = A[M,K] * B[N,K]^T
 //   mode kAllGatherGemm   column-parallel layer: A is sequence-sharded over the ranks.
-//                         A few CTAs push this rank's shard, 128 rows at a time, into
-//                         every peer's gather buffer over NVLink and raise a flag per
-//                         chunk; the GEMM CTAs start with the local rows and take up a
-//                         remote row block as soon as its flag is up, loading it by TMA
-//                         from LOCAL memory (no TMA ever reads a peer, no multicast).
+//                         Two spare warps of EVERY CTA push this rank's shard, 64 KiB
+//                         at a time, into every peer's gather buffer over NVLink and
+//                         count each piece in on the destination; the GEMM starts with
+//                         the local rows and takes up a remote 128-row block as soon as
+//                         all of its pieces are counted in, loading it by TMA from LOCAL
+//                         memory (no TMA ever reads a peer, no multicast).
 //   mode kGemmReduceScatter  row-parallel layer: every output tile is a partial sum.
-//                         The epilogue converts the accumulator tile and stores it
-//                         straight into the owning rank's partial buffer (remote owners
-//                         first), counts it in on that rank, and each rank finally sums
-//                         the partial slices of its own rows in fp32.
+//                         The epilogue converts the accumulator tile, transposes it
+//                         through shared memory so that every store instruction writes
+//                         whole 128-byte lines, and stores it straight into the owning
+//                         rank's partial buffer (remote owners first), counts it in on
+//                         that rank, and each rank finally sums the partial slices of
+//                         its own rows in fp32.
 //
-// One persistent CTA per SM, 192 threads: warp 0 issues TMA, warp 1 issues MMA, warps
-// 2-5 run the epilogue (one TMEM lane quarter each).  Tile 128 x 256 x 64, four
-// shared-memory stages, two accumulator buffers in TMEM so that the epilogue of one tile
-// overlaps the main loop of the next.  Every wait (mbarrier, flag, counter) is bounded:
-// on a timeout the CTA raises an abort flag, reports through the status block, lets its
-// other warps fall out of their loops, frees its TMEM and returns.
+// Two flavours of the same kernel.  PAIR=false: every CTA owns a 128 x 256 tile
+// (cta_group::1).  PAIR=true: the two CTAs of a cluster share a 256 x 256 tile
+// (cta_group::2): each loads its own 128 rows of A and 128 of the 256 rows of B, the
+// leader CTA issues one MMA that reads both CTAs' shared memory and writes 128
+// accumulator rows into each CTA's TMEM -- a third less operand traffic per flop.
+//
+// One persistent CTA per SM, 256 threads: warp 0 issues TMA, warp 1 issues MMA, warps
+// 2-5 run the epilogue (one TMEM lane quarter each), warps 6-7 push (all-gather mode).
+// Tile 128 x 256 x 64, four shared-memory stages, two accumulator buffers in TMEM so
+// that the epilogue of one tile overlaps the main loop of the next.  Every wait
+// (mbarrier, flag, counter) is bounded: on a timeout the CTA raises an abort flag,
+// reports through the status block, lets its other warps fall out of their loops, frees
+// its TMEM and returns.
 //
 // The FlagCX project contains no GEMM; the comparison target is NCCL all-gather /
 // reduce-scatter followed or preceded by a cuBLAS GEMM.
@@ -37,15 +47,19 @@ namespace {
 using bf16 = __nv_bfloat16;
 using namespace tc;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int kThreads = 192;
-constexpr uint32_t kStageBytes = (BM + BN) * BK * 2;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitLimitNs = 4000000000ull; // 4 s
+constexpr int kEpiCols = 64;                                // columns staged per epilogue step
 
+template <bool PAIR>
 struct __align__(1024) Smem {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int BROWS = PAIR ? BN / 2 : BN; // rows of B this CTA loads per stage
   bf16 a[STAGES][BM * BK];
-  bf16 b[STAGES][BN * BK];
+  bf16 b[STAGES][BROWS * BK];
+  uint4 epi[4][32 * kEpiCols * 2 / 16]; // per epilogue warp: 32 rows x 64 bf16, 16-byte chunks swizzled
   uint64_t full[STAGES], empty[STAGES], tmemFull[2], tmemEmpty[2];
   uint32_t tmemBase;
   int abortFlag;
@@ -53,12 +67,12 @@ struct __align__(1024) Smem {
 
 // Which row block (of 128 rows) a CTA's i-th tile covers: remote-owned blocks are
 // rotated so that every rank starts with different peers / with its own rows.
-__device__ __forceinline__ void tileCoords(const TpGemmArgs &a, int rank, int tile, int tilesN, int *tm, int *tn) {
+__device__ __forceinline__ void tileCoords(const TpGemmArgs &a, int rank, int tile, int tilesN, int TM, int *tm, int *tn) {
   int rb = tile / tilesN;
   *tn = tile % tilesN;
-  const int blocks = a.M / BM;
-  if (a.mode == kAllGatherGemm) rb = (rb + rank * (a.rowsPerRank / BM)) % blocks;           // own rows first
-  else if (a.mode == kGemmReduceScatter) rb = (rb + (rank + 1) * (a.rowsPerRank / BM)) % blocks; // own rows last
+  const int blocks = a.M / TM;
+  if (a.mode == kAllGatherGemm) rb = (rb + rank * (a.rowsPerRank / TM)) % blocks;           // own rows first
+  else if (a.mode == kGemmReduceScatter) rb = (rb + (rank + 1) * (a.rowsPerRank / TM)) % blocks; // own rows last
   *tm = rb;
 }
 
@@ -81,28 +95,35 @@ __device__ __forceinline__ bool waitFlagGe(const flagcxDevComm &c, const unsigne
   }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
     tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const flagcxDevComm c, const TpGemmArgs a) {
   extern __shared__ uint8_t rawSmem[];
-  Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~(uintptr_t)1023);
+  using SmemT = Smem<PAIR>;
+  constexpr int STAGES = SmemT::STAGES;
+  constexpr uint32_t kStageBytes = ((PAIR ? 2 * BM : BM) + BN) * BK * 2; // per stage; a pair loads 256 rows of A
+  SmemT &s = *reinterpret_cast<SmemT *>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~(uintptr_t)1023);
+  const uint32_t ctaRank = PAIR ? clusterCtaRank() : 0; // position inside the CTA pair
+  const bool leader = ctaRank == 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = c.rank, n = c.nRanks;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbarInit(&s.full[i], 1); mbarInit(&s.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], PAIR ? 8 : 4); }
     s.abortFlag = 0;
     mbarInitFence();
     prefetchTensorMap(&tmA);
     prefetchTensorMap(&tmB);
   }
   if (warp == 1) {
-    tmemAlloc(&s.tmemBase, kTmemCols);
-    tmemRelinquish();
+    if (PAIR) { tmemAllocPair(&s.tmemBase, kTmemCols); tmemRelinquishPair(); }
+    else { tmemAlloc(&s.tmemBase, kTmemCols); tmemRelinquish(); }
   }
   fenceBeforeSync();
   __syncthreads();
+  if (PAIR) clusterSync(); // the partner's barriers exist before anything is signalled on them
   fenceAfterSync();
   const uint32_t tmemBase = s.tmemBase;
   volatile int *abortFlag = &s.abortFlag;
@@ -115,66 +136,61 @@ __global__ void __launch_bounds__(kThreads, 1)
     alive = bar.sync(flagcxCoopBlock());
   }
 
-  const int nGemmCtas = gridDim.x - a.nPushCtas;
+  const int G = gridDim.x;
+  // a scheduling unit is a CTA (128-row tiles) or a CTA pair (256-row tiles)
+  const int unit = PAIR ? blockIdx.x / 2 : blockIdx.x, units = PAIR ? G / 2 : G;
+  const int TM = PAIR ? 2 * BM : BM;
   const int tilesN = a.N / BN;
-  const int nTiles = (a.M / BM) * tilesN;
+  const int nTiles = (a.M / TM) * tilesN;
   const int kBlocks = a.K / BK;
 
   if (!alive) {
     // fall through to the common exit
-  } else if ((int)blockIdx.x >= nGemmCtas) {
-    // ---- pusher CTAs (all-gather mode): my shard -> every peer, chunk by chunk ----
-    const int j = blockIdx.x - nGemmCtas;
-    const int chunks = a.rowsPerRank / BM;
-    const size_t chunkBytes = (size_t)BM * a.K * 2;
-    const char *src = (const char *)(a.gathered[rank] + (size_t)rank * a.rowsPerRank * a.K);
-    for (int ch = j; ch < chunks && !*abortFlag; ch += a.nPushCtas) {
-      for (int k = 1; k < n; ++k) {
-        int p = rank + k; if (p >= n) p -= n;
-        char *dst = (char *)(a.gathered[p] + (size_t)rank * a.rowsPerRank * a.K) + ch * chunkBytes;
-        ctaCopy(dst, src + ch * chunkBytes, 0, chunkBytes);
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          fcxdev::fenceSys();
-          fcxdev::stReleaseSys(a.chunkFlags[p] + (size_t)rank * chunks + ch, a.epoch);
-        }
-      }
-    }
   } else if (warp == 0) {
     // ---- TMA producer ----
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < nTiles && ok; tile += nGemmCtas) {
+      for (int tile = unit; tile < nTiles && ok; tile += units) {
         int tm, tn;
-        tileCoords(a, rank, tile, tilesN, &tm, &tn);
+        tileCoords(a, rank, tile, tilesN, TM, &tm, &tn);
+        const int arow = tm * TM + (int)ctaRank * BM; // first row of A this CTA loads
         if (a.mode == kAllGatherGemm && n > 1) {
           const int chunks = a.rowsPerRank / BM;
-          const int owner = tm / chunks;
+          const int owner = arow / a.rowsPerRank;
           if (owner != rank) {
-            ok = waitFlagGe(c, a.chunkFlags[rank] + (size_t)owner * chunks + tm % chunks, a.epoch, abortFlag, owner);
+            ok = waitFlagGe(c, a.chunkFlags[rank] + (size_t)owner * chunks + (arow / BM) % chunks,
+                            a.epoch * (unsigned long long)a.piecesPerChunk, abortFlag, owner);
             fenceProxyAsync(); // the rows were written by a peer's stores; TMA reads them next
             if (!ok) break;
           }
         }
         for (int kb = 0; kb < kBlocks; ++kb) {
           if (!mbarWait(&s.empty[stage], phase ^ 1, abortFlag, kWaitLimitNs)) { ok = false; break; }
-          mbarExpectTx(&s.full[stage], kStageBytes);
-          tmaLoad2d(s.a[stage], &tmA, kb * BK, tm * BM, &s.full[stage]);
-          tmaLoad2d(s.b[stage], &tmB, kb * BK, tn * BN, &s.full[stage]);
+          if (PAIR) {
+            // both CTAs' loads are counted on the leader's barrier, which the MMA waits on
+            if (leader) mbarExpectTx(&s.full[stage], kStageBytes);
+            const uint32_t bar = mapToCta(smemAddr(&s.full[stage]), 0);
+            tmaLoad2dPair(s.a[stage], &tmA, kb * BK, arow, bar);
+            tmaLoad2dPair(s.b[stage], &tmB, kb * BK, tn * BN + (int)ctaRank * (BN / 2), bar);
+          } else {
+            mbarExpectTx(&s.full[stage], kStageBytes);
+            tmaLoad2d(s.a[stage], &tmA, kb * BK, arow, &s.full[stage]);
+            tmaLoad2d(s.b[stage], &tmB, kb * BK, tn * BN, &s.full[stage]);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
-    if (lane == 0) {
-      constexpr uint32_t idesc = instrDescBf16(BM, BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = instrDescBf16(PAIR ? 2 * BM : BM, BN);
       int stage = 0, acc = 0;
       uint32_t phase = 0, accPhase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < nTiles && ok; tile += nGemmCtas) {
+      for (int tile = unit; tile < nTiles && ok; tile += units) {
         if (!mbarWait(&s.tmemEmpty[acc], accPhase ^ 1, abortFlag, kWaitLimitNs)) break;
         fenceAfterSync();
         for (int kb = 0; kb < kBlocks; ++kb) {
@@ -182,62 +198,117 @@ __global__ void __launch_bounds__(kThreads, 1)
           fenceAfterSync();
           const uint64_t da = smemDescSw128(s.a[stage]), db = smemDescSw128(s.b[stage]);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4) // 16 bf16 = 32 bytes along K inside the swizzled row
-            mmaBf16(tmemBase + acc * BN, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
-          mmaCommit(&s.empty[stage]); // stage may be refilled once these MMAs have read it
+          for (int k4 = 0; k4 < BK / 16; ++k4) { // 16 bf16 = 32 bytes along K inside the swizzled row
+            if (PAIR) mmaBf16Pair(tmemBase + acc * BN, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+            else mmaBf16(tmemBase + acc * BN, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0);
+          }
+          // the stage may be refilled (in both CTAs) once these MMAs have read it
+          if (PAIR) mmaCommitPair(&s.empty[stage], 3); else mmaCommit(&s.empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        mmaCommit(&s.tmemFull[acc]);
+        if (PAIR) mmaCommitPair(&s.tmemFull[acc], 3); else mmaCommit(&s.tmemFull[acc]);
         if (++acc == 2) { acc = 0; accPhase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
     const int q = warp & 3;
+    uint4 *stg = s.epi[warp - 2];
     int acc = 0;
     uint32_t accPhase = 0;
-    for (int tile = blockIdx.x; tile < nTiles; tile += nGemmCtas) {
+    for (int tile = unit; tile < nTiles; tile += units) {
       int tm, tn;
-      tileCoords(a, rank, tile, tilesN, &tm, &tn);
+      tileCoords(a, rank, tile, tilesN, TM, &tm, &tn);
       if (!mbarWait(&s.tmemFull[acc], accPhase, abortFlag, kWaitLimitNs)) break;
       fenceAfterSync();
-      const int rowInTile = q * 32 + lane;
-      const size_t grow = (size_t)tm * BM + rowInTile;
-      bf16 *drow;
+      // rows q*32 .. q*32+31 of the tile belong to this warp; all of them have one owner
+      const size_t growBase = (size_t)tm * TM + ctaRank * BM + q * 32;
+      bf16 *dbase;
       int owner = rank;
       if (a.mode == kGemmReduceScatter) {
-        owner = (int)(grow / a.rowsPerRank);
-        drow = a.partial[owner] + ((size_t)rank * a.rowsPerRank + (grow - (size_t)owner * a.rowsPerRank)) * a.N;
+        owner = (int)(growBase / a.rowsPerRank);
+        dbase = a.partial[owner] + ((size_t)rank * a.rowsPerRank + (growBase - (size_t)owner * a.rowsPerRank)) * a.N;
       } else {
-        drow = a.D + grow * a.N;
+        dbase = a.D + growBase * a.N;
       }
-      drow += (size_t)tn * BN;
+      dbase += (size_t)tn * BN;
 #pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
-        uint32_t r[32];
-        tmemLoad32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + cb * 32, r);
-        tmemLoadWait();
-        uint4 o[4];
-        bf16 *ob = (bf16 *)o;
+      for (int cb = 0; cb < BN / kEpiCols; ++cb) {
+        // this thread's row, 64 fp32 columns -> 64 bf16 = eight 16-byte chunks, swizzled into the staging
 #pragma unroll
-        for (int i = 0; i < 32; ++i) ob[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmemLoad32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + cb * kEpiCols + h * 32, r);
+          tmemLoadWait();
+          uint4 o[4];
+          bf16 *ob = (bf16 *)o;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) st16((uint4 *)(drow + cb * 32) + i, o[i]);
+          for (int i = 0; i < 32; ++i) ob[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) stg[lane * 8 + ((h * 4 + i) ^ (lane & 7))] = o[i];
+        }
+        __syncwarp();
+        // read back transposed: one instruction stores four rows x 128 contiguous bytes
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int row = k * 4 + (lane >> 3), ch = lane & 7;
+          uint4 v = stg[row * 8 + (ch ^ (row & 7))];
+          st16((uint4 *)(dbase + (size_t)row * a.N + cb * kEpiCols) + ch, v);
+        }
+        __syncwarp();
       }
       fenceBeforeSync();
       __syncwarp();
-      if (lane == 0) mbarArrive(&s.tmemEmpty[acc]);
+      if (lane == 0) {
+        // the accumulator buffer is free again: tell the CTA that issues the MMAs
+        if (PAIR && !leader) mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
+        else mbarArrive(&s.tmemEmpty[acc]);
+      }
       if (a.mode == kGemmReduceScatter) {
         // count the tile in on its owner once all four epilogue warps have stored it
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           fcxdev::fenceSys();
-          const int rbLocal = (int)((grow - (size_t)owner * a.rowsPerRank) / BM);
+          const int rbLocal = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
           fcxdev::redAddReleaseSys(a.rowFlags[owner] + rbLocal, 1ull);
         }
       }
       if (++acc == 2) { acc = 0; accPhase ^= 1; }
+    }
+  } else if (a.mode == kAllGatherGemm && n > 1) {
+    // ---- pusher warps 6..7: my shard -> every peer, piece by piece, chunk 0 first ----
+    const int t = threadIdx.x - 192; // 0..63
+    const int chunks = a.rowsPerRank / BM;
+    const size_t chunkBytes = (size_t)BM * a.K * 2;
+    const size_t pieceBytes = chunkBytes / a.piecesPerChunk;
+    const size_t shardOff = (size_t)rank * a.rowsPerRank * a.K * 2;
+    const char *src = (const char *)a.gathered[rank] + shardOff;
+    const int itemsPerChunk = (n - 1) * a.piecesPerChunk;
+    const int items = chunks * itemsPerChunk;
+    for (int u = blockIdx.x; u < items && !*abortFlag; u += G) {
+      const int ch = u / itemsPerChunk, rem = u % itemsPerChunk;
+      const int piece = rem / (n - 1);
+      int p = rank + 1 + rem % (n - 1);
+      if (p >= n) p -= n;
+      const size_t off = ch * chunkBytes + piece * pieceBytes;
+      const uint4 *sv = (const uint4 *)(src + off);
+      uint4 *dv = (uint4 *)((char *)a.gathered[p] + shardOff + off);
+      const size_t nv = pieceBytes >> 4;
+      size_t i = t;
+      for (; i + 7 * 64 < nv; i += 8 * 64) {
+        uint4 r[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = ldLocal16(sv + i + k * 64);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) st16(dv + i + k * 64, r[k]);
+      }
+      for (; i < nv; i += 64) st16(dv + i, ldLocal16(sv + i));
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      if (t == 0) {
+        fcxdev::fenceSys();
+        fcxdev::redAddReleaseSys(a.chunkFlags[p] + (size_t)rank * chunks + ch, 1ull);
+      }
     }
   }
 
@@ -253,14 +324,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (threadIdx.x == 0) ok = waitFlagGe(c, a.rowFlags[rank] + rb, want, abortFlag, 0xffffffffu);
       if (__syncthreads_or(ok ? 0 : 1)) break;
       const size_t base = (size_t)rb * BM * a.N, packs = (size_t)BM * a.N / 8;
-      for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < packs; i += (size_t)gridDim.x * kThreads) {
-        float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int sidx = 0; sidx < n; ++sidx) {
-          uint4 v = ldSys16(a.partial[rank] + sidx * sliceElems + base + i * 8);
-          const bf16 *e = (const bf16 *)&v;
+      for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < packs; i += (size_t)G * kThreads) {
+        uint4 v[FLAGCX_MAX_RANKS];
 #pragma unroll
-          for (int t = 0; t < 8; ++t) accv[t] += __bfloat162float(e[t]);
-        }
+        for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
+          if (sidx < n) v[sidx] = ldSys16(a.partial[rank] + sidx * sliceElems + base + i * 8);
+        float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
+          if (sidx < n) {
+            const bf16 *e = (const bf16 *)&v[sidx];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) accv[t] += __bfloat162float(e[t]);
+          }
         uint4 o;
         bf16 *oe = (bf16 *)&o;
 #pragma unroll
@@ -272,23 +348,44 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0 && *abortFlag)
     fcxdev::reportError(c.status, FLAGCX_DEV_TIMEOUT, FLAGCX_DEV_AT_KERNEL, (unsigned)blockIdx.x, 0);
   __syncthreads();
-  if (warp == 1) tmemDealloc(tmemBase, kTmemCols);
+  if (PAIR) clusterSync(); // neither CTA leaves while its partner may still signal it
+  if (warp == 1) {
+    if (PAIR) tmemDeallocPair(tmemBase, kTmemCols); else tmemDealloc(tmemBase, kTmemCols);
+  }
 }
 
 } // namespace
 
-size_t tpGemmSmemBytes() { return sizeof(Smem) + 1024; }
+size_t tpGemmSmemBytes(bool pair) { return (pair ? sizeof(Smem<true>) : sizeof(Smem<false>)) + 1024; }
 
+// pair: use CTA pairs (cluster of two, 256 x 256 tiles); needs an even grid and M a
+// multiple of 256 (per rank in the fused modes).
 cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const flagcxDevComm &c,
-                         const TpGemmArgs &a, int nCtas) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tpGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmSmemBytes());
+                         const TpGemmArgs &a, int nCtas, bool pair) {
+  static bool configured[2] = {false, false};
+  const void *fn = pair ? (const void *)tpGemmKernel<true> : (const void *)tpGemmKernel<false>;
+  if (!configured[pair]) {
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tpGemmSmemBytes(pair));
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[pair] = true;
   }
-  tpGemmKernel<<<nCtas, kThreads, tpGemmSmemBytes(), stream>>>(tmA, tmB, c, a);
-  return cudaGetLastError();
+  if (!pair) {
+    tpGemmKernel<false><<<nCtas, kThreads, tpGemmSmemBytes(false), stream>>>(tmA, tmB, c, a);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nCtas & ~1);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = tpGemmSmemBytes(true);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, tpGemmKernel<true>, tmA, tmB, c, a);
 }
 
 } // namespace fcx

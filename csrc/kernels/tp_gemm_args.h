@@ -13,7 +13,7 @@ struct TpGemmArgs {
   __nv_bfloat16 *D; // [M, N] output (plain, all-gather modes)
   int M, N, K, mode;
   int rowsPerRank;  // M / nRanks
-  int nPushCtas;    // CTAs that push the local shard (all-gather mode)
+  int piecesPerChunk; // all-gather mode: a 128-row chunk travels in this many pieces per peer
   unsigned long long epoch; // call counter of this handle, starts at 1
   // all-gather -> GEMM
   __nv_bfloat16 *gathered[FLAGCX_MAX_RANKS];      // rank p's gather buffer [M, K] as mapped here

@@ -9,8 +9,11 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (1024, 3584, 1024),
                                    (2048, 1024, 8192)])
-def test_tcgen05_gemm_matches_fp32_reference(M, N, K):
+@pytest.mark.parametrize("pair", [1, 0])
+def test_tcgen05_gemm_matches_fp32_reference(M, N, K, pair, monkeypatch):
+    """pair=1: CTA pairs (cta_group::2, 256-row tiles) where M allows; pair=0: single CTAs."""
     from flagcx_b200.parallel.tp import gemm_bf16
+    monkeypatch.setenv("FLAGCX_GEMM_PAIR", str(pair))
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
     b = (torch.randn(N, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
