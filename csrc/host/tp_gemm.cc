@@ -33,6 +33,10 @@ namespace {
 // CTA pairs (256-row tiles, cta_group::2) whenever the row blocks allow it.
 bool usePair(int rowsPerOwner) { return readParam("GEMM_PAIR", 1) != 0 && rowsPerOwner % 256 == 0; }
 
+// Row blocks walked together by the tile order: the grid (74 pairs or 148 CTAs) then
+// covers a near-square patch of the output at any moment.
+int groupRows(bool pair) { return std::max(1, (int)readParam("GEMM_GROUP", pair ? 8 : 16)); }
+
 int smCount() {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -104,6 +108,7 @@ flagcxResult_t flagcxGemmBf16(const void *A, const void *B, void *D, int M, int 
   a.M = M; a.N = N; a.K = K;
   a.mode = kPlain;
   a.rowsPerRank = M;
+  a.groupRows = groupRows(pair);
   int tiles = (M / 128) * (N / 256);
   if (pair) tiles = 2 * ((M / 256) * (N / 256));
   cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, ta, tb, c, a, std::min(tiles, smCount()), pair);
@@ -167,6 +172,7 @@ flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t h, const void *B, void *D, f
   a.M = h->M; a.N = h->N; a.K = h->K;
   a.mode = kAllGatherGemm;
   a.rowsPerRank = h->rowsPerRank;
+  a.groupRows = groupRows(pair);
   a.epoch = ++h->epoch;
   for (int p = 0; p < c->nranks; ++p) {
     a.gathered[p] = (__nv_bfloat16 *)h->wBuf->peer[p];
@@ -196,6 +202,7 @@ flagcxResult_t flagcxTpGemmReduceScatter(flagcxTpGemm_t h, const void *A, const 
   a.M = h->M; a.N = h->N; a.K = h->K;
   a.mode = kGemmReduceScatter;
   a.rowsPerRank = h->rowsPerRank;
+  a.groupRows = groupRows(pair);
   a.epoch = ++h->epoch;
   a.out = (__nv_bfloat16 *)out;
   for (int p = 0; p < c->nranks; ++p) {

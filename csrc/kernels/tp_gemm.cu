@@ -26,8 +26,9 @@
 //
 // One persistent CTA per SM, 256 threads: warp 0 issues TMA, warp 1 issues MMA, warps
 // 2-5 run the epilogue (one TMEM lane quarter each), warps 6-7 push (all-gather mode).
-// Tile 128 x 256 x 64, four shared-memory stages, two accumulator buffers in TMEM so
-// that the epilogue of one tile overlaps the main loop of the next.  Every wait
+// K step 64, four (single CTA) or six (pair) shared-memory stages, two accumulator
+// buffers in TMEM so that the epilogue of one tile overlaps the main loop of the next.
+// Tiles are walked in compact groups (see tileCoords) for L2 reuse.  Every wait
 // (mbarrier, flag, counter) is bounded: on a timeout the CTA raises an abort flag,
 // reports through the status block, lets its other warps fall out of their loops, frees
 // its TMEM and returns.
@@ -65,14 +66,22 @@ struct __align__(1024) Smem {
   int abortFlag;
 };
 
-// Which row block (of 128 rows) a CTA's i-th tile covers: remote-owned blocks are
-// rotated so that every rank starts with different peers / with its own rows.
+// Which tile the grid's i-th scheduling slot covers.  Rank by rank (remote-owned row
+// blocks rotated so that every rank starts with its own rows / with a different
+// peer's), and inside one rank's rows in groups of `groupRows` row blocks that are
+// walked column by column: the tiles in flight at any moment then form a compact
+// rectangle (about 8 x 9 tiles of 256 x 256) instead of a one-tile-high stripe, so the
+// rows of A and B that they share are fetched from HBM once and hit in L2 afterwards.
 __device__ __forceinline__ void tileCoords(const TpGemmArgs &a, int rank, int tile, int tilesN, int TM, int *tm, int *tn) {
-  int rb = tile / tilesN;
-  *tn = tile % tilesN;
-  const int blocks = a.M / TM;
-  if (a.mode == kAllGatherGemm) rb = (rb + rank * (a.rowsPerRank / TM)) % blocks;           // own rows first
-  else if (a.mode == kGemmReduceScatter) rb = (rb + (rank + 1) * (a.rowsPerRank / TM)) % blocks; // own rows last
+  const int blocks = a.M / TM, bpr = a.rowsPerRank / TM, tilesPerRank = bpr * tilesN;
+  const int r = tile / tilesPerRank, w = tile - r * tilesPerRank;
+  const int perGroup = a.groupRows * tilesN;
+  const int g = w / perGroup, wg = w - g * perGroup;
+  const int gsize = min(a.groupRows, bpr - g * a.groupRows);
+  *tn = wg / gsize;
+  int rb = r * bpr + g * a.groupRows + (wg - *tn * gsize);
+  if (a.mode == kAllGatherGemm) rb = (rb + rank * bpr) % blocks;                 // own rows first
+  else if (a.mode == kGemmReduceScatter) rb = (rb + (rank + 1) * bpr) % blocks; // own rows last
   *tm = rb;
 }
 

@@ -14,6 +14,7 @@ struct TpGemmArgs {
   int M, N, K, mode;
   int rowsPerRank;  // M / nRanks
   int piecesPerChunk; // all-gather mode: a 128-row chunk travels in this many pieces per peer
+  int groupRows;      // tile order: this many row blocks are walked together, column by column
   unsigned long long epoch; // call counter of this handle, starts at 1
   // all-gather -> GEMM
   __nv_bfloat16 *gathered[FLAGCX_MAX_RANKS];      // rank p's gather buffer [M, K] as mapped here
