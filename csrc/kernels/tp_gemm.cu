@@ -14,9 +14,11 @@
 //                         The epilogue converts the accumulator tile, transposes it
 //                         through shared memory so that every store instruction writes
 //                         whole 128-byte lines, and stores it straight into the owning
-//                         rank's partial buffer (remote owners first), counts it in on
-//                         that rank, and each rank finally sums the partial slices of
-//                         its own rows in fp32.
+//                         rank's partial buffer (remote owners first) and counts it in
+//                         on that rank.  A rank's own rows come last: their epilogue
+//                         waits for the peers' counts, adds the peers' partial tiles
+//                         (local memory by then) in fp32 and stores the final rows --
+//                         there is no separate reduction pass.
 //
 // Two flavours of the same kernel.  PAIR=false: every CTA owns a 128 x 256 tile
 // (cta_group::1).  PAIR=true: the two CTAs of a cluster share a 256 x 256 tile
@@ -235,13 +237,31 @@ __global__ void __launch_bounds__(kThreads, 1)
       const size_t growBase = (size_t)tm * TM + ctaRank * BM + q * 32;
       bf16 *dbase;
       int owner = rank;
+      const bf16 *others = nullptr; // reduce-scatter, own rows: slice 0 of the partial sums of these rows
       if (a.mode == kGemmReduceScatter) {
         owner = (int)(growBase / a.rowsPerRank);
-        dbase = a.partial[owner] + ((size_t)rank * a.rowsPerRank + (growBase - (size_t)owner * a.rowsPerRank)) * a.N;
+        const size_t rowLocal = growBase - (size_t)owner * a.rowsPerRank;
+        if (owner != rank) {
+          dbase = a.partial[owner] + ((size_t)rank * a.rowsPerRank + rowLocal) * a.N;
+        } else {
+          // My own rows come last in the tile order, when the peers' partial sums of them
+          // have (nearly) all landed here: wait for the row block's counter, then add
+          // them to the accumulator tile on its way out and store the final rows.
+          dbase = a.out + rowLocal * a.N;
+          if (n > 1) {
+            bool ok = true;
+            if (lane == 0)
+              ok = waitFlagGe(c, a.rowFlags[rank] + rowLocal / BM,
+                              a.epoch * (unsigned long long)((n - 1) * tilesN), abortFlag, 0xffffffffu);
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+            others = a.partial[rank] + rowLocal * a.N + (size_t)tn * BN;
+          }
+        }
       } else {
         dbase = a.D + growBase * a.N;
       }
       dbase += (size_t)tn * BN;
+      const size_t sliceElems = (size_t)a.rowsPerRank * a.N;
 #pragma unroll 1
       for (int cb = 0; cb < BN / kEpiCols; ++cb) {
         // this thread's row, 64 fp32 columns -> 64 bf16 = eight 16-byte chunks, swizzled into the staging
@@ -259,11 +279,40 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
         // read back transposed: one instruction stores four rows x 128 contiguous bytes
+        if (others == nullptr) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int row = k * 4 + (lane >> 3), ch = lane & 7;
-          uint4 v = stg[row * 8 + (ch ^ (row & 7))];
-          st16((uint4 *)(dbase + (size_t)row * a.N + cb * kEpiCols) + ch, v);
+          for (int k = 0; k < 8; ++k) {
+            const int row = k * 4 + (lane >> 3), ch = lane & 7;
+            uint4 v = stg[row * 8 + (ch ^ (row & 7))];
+            st16((uint4 *)(dbase + (size_t)row * a.N + cb * kEpiCols) + ch, v);
+          }
+        } else {
+#pragma unroll 2
+          for (int k = 0; k < 8; ++k) {
+            const int row = k * 4 + (lane >> 3), ch = lane & 7;
+            const bf16 *src = others + (size_t)row * a.N + cb * kEpiCols + ch * 8;
+            uint4 p[FLAGCX_MAX_RANKS];
+#pragma unroll
+            for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
+              if (sidx < n && sidx != rank) p[sidx] = ldSys16(src + (size_t)sidx * sliceElems);
+            uint4 v = stg[row * 8 + (ch ^ (row & 7))];
+            float accv[8];
+            const bf16 *ve = (const bf16 *)&v;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) accv[t] = __bfloat162float(ve[t]);
+            // fixed rank order except that this rank's own term comes first
+#pragma unroll
+            for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
+              if (sidx < n && sidx != rank) {
+                const bf16 *e = (const bf16 *)&p[sidx];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) accv[t] += __bfloat162float(e[t]);
+              }
+            bf16 *oe = (bf16 *)&v;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) oe[t] = __float2bfloat16_rn(accv[t]);
+            st16((uint4 *)(dbase + (size_t)row * a.N + cb * kEpiCols) + ch, v);
+          }
         }
         __syncwarp();
       }
@@ -274,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (PAIR && !leader) mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
         else mbarArrive(&s.tmemEmpty[acc]);
       }
-      if (a.mode == kGemmReduceScatter) {
+      if (a.mode == kGemmReduceScatter && owner != rank) {
         // count the tile in on its owner once all four epilogue warps have stored it
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
@@ -322,38 +371,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 
   __syncthreads();
-  if (a.mode == kGemmReduceScatter && !*abortFlag && alive) {
-    // ---- reduce my rows: sum the n partial slices in fp32, one bf16 store ----
-    const int rbs = a.rowsPerRank / BM;
-    const unsigned long long want = a.epoch * (unsigned long long)(n * tilesN);
-    const size_t sliceElems = (size_t)a.rowsPerRank * a.N;
-    // every CTA takes a share of every row block, so the whole GPU streams the slices
-    for (int rb = 0; rb < rbs; ++rb) {
-      bool ok = true;
-      if (threadIdx.x == 0) ok = waitFlagGe(c, a.rowFlags[rank] + rb, want, abortFlag, 0xffffffffu);
-      if (__syncthreads_or(ok ? 0 : 1)) break;
-      const size_t base = (size_t)rb * BM * a.N, packs = (size_t)BM * a.N / 8;
-      for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < packs; i += (size_t)G * kThreads) {
-        uint4 v[FLAGCX_MAX_RANKS];
-#pragma unroll
-        for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
-          if (sidx < n) v[sidx] = ldSys16(a.partial[rank] + sidx * sliceElems + base + i * 8);
-        float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-        for (int sidx = 0; sidx < FLAGCX_MAX_RANKS; ++sidx)
-          if (sidx < n) {
-            const bf16 *e = (const bf16 *)&v[sidx];
-#pragma unroll
-            for (int t = 0; t < 8; ++t) accv[t] += __bfloat162float(e[t]);
-          }
-        uint4 o;
-        bf16 *oe = (bf16 *)&o;
-#pragma unroll
-        for (int t = 0; t < 8; ++t) oe[t] = __float2bfloat16_rn(accv[t]);
-        st16(a.out + base + i * 8, o);
-      }
-    }
-  }
   if (threadIdx.x == 0 && *abortFlag)
     fcxdev::reportError(c.status, FLAGCX_DEV_TIMEOUT, FLAGCX_DEV_AT_KERNEL, (unsigned)blockIdx.x, 0);
   __syncthreads();
