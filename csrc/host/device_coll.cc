@@ -75,6 +75,21 @@ void initArgs(flagcxComm *c, CollArgs &a, int kind, flagcxDataType_t dt) {
     a.meta[p] = (unsigned long long *)((char *)c->internalWin->peer[p] + c->layout.metaOff);
 }
 
+// Push kinds whose blocks are large and 16-byte aligned move through the bulk-copy
+// engine (one thread per CTA drives a ring of shared-memory stages) instead of
+// per-thread loads and stores.  Returns the stage size in bytes, 0 for the thread path.
+int bulkStageFor(flagcxComm *c, const CollArgs &a) {
+  if (a.kind != kAllGatherPush && a.kind != kAllToAllPush && a.kind != kBroadcastPush) return 0;
+  // measured on B200 pairs: the engine wins (about 670 against 590 GB/s per direction)
+  // once a rank sends some tens of MB; below that its start-up costs more than it saves
+  static const int64_t enable = readParam("BULK_COPY", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 48 << 20);
+  const size_t blk = a.count * (size_t)a.elemSize;
+  if (!enable || blk * (size_t)std::max(1, c->nranks - 1) < (size_t)minBytes || blk % 16) return 0;
+  uintptr_t bits = (uintptr_t)a.in[c->rank] | a.inStride | a.outStride;
+  for (int p = 0; p < c->nranks; ++p) bits |= (uintptr_t)a.out[p];
+  return (bits & 15) ? 0 : 16384;
+}
+
 flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, cudaStream_t stream) {
   nCtas = std::max(1, std::min(nCtas, FLAGCX_COLL_BARRIER_SLOTS));
   if (c->emu) return emuSubmit(c, family, &a, nullptr, nCtas, stream);
@@ -82,9 +97,15 @@ flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, c
   lc.comm = &c->dev;
   lc.stream = stream;
   lc.nCtas = nCtas;
-  cudaError_t e = family == kFamReduce ? launchReduceKernel(lc, a, c->nranks)
-                  : family == kFamCopy ? launchCopyKernel(lc, a)
-                                       : launchNvlsKernel(lc, a);
+  cudaError_t e;
+  if (family == kFamCopy) {
+    CollArgs b = a;
+    b.bulkStage = bulkStageFor(c, a);
+    b.bulkDepth = readParam("BULK_STAGES", 8) >= 12 ? 12 : 8;
+    e = launchCopyKernel(lc, b);
+  } else {
+    e = family == kFamReduce ? launchReduceKernel(lc, a, c->nranks) : launchNvlsKernel(lc, a);
+  }
   if (e != cudaSuccess) {
     FCX_WARN("kernel launch failed: %s", cudaGetErrorString(e));
     return flagcxUnhandledDeviceError;

@@ -82,6 +82,8 @@ struct CollArgs {
   int divisor;  // integer average: divide by this (0 = none)
   int kind, dtype, elemSize, redOp, outMode, root;
   uint32_t flags;
+  int bulkDepth; // stages of that ring: 8 or 12
+  int bulkStage; // push kinds: bytes per shared-memory stage of the bulk-copy path (0: per-thread loads/stores)
   // alltoallv (element units), this rank's view
   size_t sendCounts[FLAGCX_MAX_RANKS], sendDispls[FLAGCX_MAX_RANKS];
   size_t recvCounts[FLAGCX_MAX_RANKS], recvDispls[FLAGCX_MAX_RANKS];

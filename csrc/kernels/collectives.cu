@@ -307,6 +307,110 @@ __device__ void ctaFanOut(char *const *dst, int nDst, const char *src, size_t by
   }
 }
 
+// ---- bulk-copy path of the push kinds ---------------------------------------------
+// One thread per CTA drives the copy engine: untiled bulk copies bring 16 KiB pieces
+// of LOCAL memory into a ring of shared-memory stages (completion on an mbarrier), and
+// bulk stores send each stage on to its destination(s) in peer memory.  The loads run
+// half a ring ahead of the stores; a stage is reloaded only after the stores
+// that read it have left shared memory (wait_group.read).  No load here names a
+// peer and none is multicast; sources, destinations and sizes are multiples of 16.
+constexpr int kBulkMaxStages = 12; // the ring has 8 or 12 stages; the loads run half a ring ahead
+extern __shared__ __align__(128) unsigned char bulkRing[];
+
+__device__ __forceinline__ uint32_t smem32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// K destinations; sameSrc: every piece of src[0] goes to all of them (all-gather,
+// broadcast), else piece i of src[k] goes to dst[k] (all-to-all), peers interleaved.
+// Runs in ONE thread.  Returns false after a timed-out wait.
+__device__ bool bulkMoveThread(const flagcxDevComm &c, uint64_t *full, const char *const *src, char *const *dst, int K,
+                               bool sameSrc, size_t bb, size_t be, uint32_t stageBytes, int stages) {
+  if (bb >= be || K == 0) return true;
+  const int ahead = stages / 2;
+  for (int s = 0; s < stages; ++s)
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem32(&full[s])) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
+  const size_t chunks = (be - bb + stageBytes - 1) / stageBytes;
+  const size_t items = sameSrc ? chunks : chunks * (size_t)K;
+  const uint32_t ring = smem32(bulkRing);
+
+  auto issueLoad = [&](size_t it) {
+    const size_t ch = sameSrc ? it : it / K;
+    const int k = sameSrc ? 0 : (int)(it % K);
+    const size_t off = bb + ch * stageBytes;
+    const uint32_t sz = (uint32_t)((be - off) < stageBytes ? (be - off) : stageBytes);
+    const int s = (int)(it % stages);
+    const uint32_t bar = smem32(&full[s]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(sz) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     ring + s * stageBytes),
+                 "l"(src[k] + off), "r"(sz), "r"(bar)
+                 : "memory");
+  };
+
+  for (size_t it = 0; it < items && it < (size_t)ahead; ++it) issueLoad(it);
+  bool ok = true;
+  for (size_t it = 0; it < items; ++it) {
+    if (it + ahead < items) {
+      // the stage about to be reloaded was last read by the stores of item it+ahead-stages
+      // (at most stages - ahead - 1 younger store groups may still be reading)
+      if (stages == 8) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+      else asm volatile("cp.async.bulk.wait_group.read 5;" ::: "memory");
+      issueLoad(it + ahead);
+    }
+    const int s = (int)(it % stages);
+    const uint32_t bar = smem32(&full[s]), parity = (uint32_t)(it / stages) & 1u;
+    uint32_t done = 0;
+    unsigned long long t0 = 0;
+    for (unsigned spins = 0; !done; ++spins) {
+      asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                   : "=r"(done)
+                   : "r"(bar), "r"(parity)
+                   : "memory");
+      if (!done && (spins & 255u) == 255u) {
+        if (t0 == 0) t0 = fcxdev::globalTimerNs();
+        else if (fcxdev::globalTimerNs() - t0 > c.timeoutNs) { ok = false; break; }
+      }
+    }
+    if (!ok) {
+      fcxdev::reportError(c.status, FLAGCX_DEV_TIMEOUT, FLAGCX_DEV_AT_KERNEL, (unsigned)blockIdx.x, it);
+      break;
+    }
+    const size_t ch = sameSrc ? it : it / K;
+    const size_t off = bb + ch * stageBytes;
+    const uint32_t sz = (uint32_t)((be - off) < stageBytes ? (be - off) : stageBytes);
+    const uint32_t from = ring + s * stageBytes;
+    if (sameSrc) {
+      for (int k = 0; k < K; ++k)
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst[k] + off), "r"(from), "r"(sz)
+                     : "memory");
+    } else {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst[it % K] + off), "r"(from),
+                   "r"(sz)
+                   : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  }
+  // every store has been written before the closing barrier releases the peers
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return ok;
+}
+
+// All threads call this; returns false (in all of them) after a timed-out wait.
+__device__ bool ctaBulkMove(const flagcxDevComm &c, const char *const *src, char *const *dst, int K, bool sameSrc,
+                            size_t bytes, int b, int g, uint32_t stageBytes, int stages) {
+  __shared__ __align__(8) uint64_t full[kBulkMaxStages];
+  __shared__ int okShared;
+  size_t ub, ue;
+  ctaShare(bytes >> 4, b, g, &ub, &ue);
+  asm volatile("fence.proxy.async;" ::: "memory"); // a copy-in by this CTA's threads precedes the engine's reads
+  __syncthreads();
+  if (threadIdx.x == 0) okShared = bulkMoveThread(c, full, src, dst, K, sameSrc, ub << 4, ue << 4, stageBytes, stages) ? 1 : 0;
+  __syncthreads();
+  return okShared != 0;
+}
+
 __device__ void ctaCopyShare(char *dst, const char *src, size_t bytes, int b, int g) {
   size_t ub, ue;
   ctaShare((bytes + 15) >> 4, b, g, &ub, &ue);
@@ -342,7 +446,12 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
         if (p == rank && d == a.in[rank]) continue; // in place
         dst[nd++] = d;
       }
-      ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+      if (a.bulkStage) {
+        const char *src0 = a.in[rank];
+        if (!ctaBulkMove(c, &src0, dst, nd, true, blk, b, g, a.bulkStage, a.bulkDepth)) return;
+      } else {
+        ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+      }
       break;
     }
     case kAllGatherPull:
@@ -362,7 +471,12 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
           if (p == rank && a.in[rank] == a.out[rank]) continue;
           dst[nd++] = a.out[p];
         }
-        ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+        if (a.bulkStage) {
+          const char *src0 = a.in[rank];
+          if (!ctaBulkMove(c, &src0, dst, nd, true, blk, b, g, a.bulkStage, a.bulkDepth)) return;
+        } else {
+          ctaFanOut(dst, nd, a.in[rank], blk, b, g);
+        }
       }
       break;
     case kBroadcastPull:
@@ -395,6 +509,10 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
           dst[k] = a.out[rank] + a.outStride * p;
         }
         vec &= ((((uintptr_t)src[k]) | ((uintptr_t)dst[k])) & 15) == 0;
+      }
+      if (a.bulkStage && a.kind == kAllToAllPush) {
+        if (!ctaBulkMove(c, src, dst, n, false, blk, b, g, a.bulkStage, a.bulkDepth)) return;
+        break;
       }
       if (!vec) {
         for (int k = 0; k < n; ++k) ctaCopyShare(dst[k], src[k], blk, b, g);
@@ -705,7 +823,17 @@ cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a) {
     void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
     return cudaLaunchCooperativeKernel((const void *)copyKernelEmu, grid, block, params, 0, lc.stream);
   }
-  copyKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  size_t smem = 0;
+  if (a.bulkStage) {
+    smem = (size_t)a.bulkStage * kBulkMaxStages;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(copyKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+  }
+  copyKernel<<<grid, block, smem, lc.stream>>>(*lc.comm, a);
   return cudaGetLastError();
 }
 

@@ -18,10 +18,14 @@ needs2 = pytest.mark.skipif(ngpus() < 2, reason="needs at least 2 GPUs")
 
 @needs2
 @pytest.mark.parametrize("registered", [True, False])
-def test_device_collectives_on_real_peers(registered):
+@pytest.mark.parametrize("count", [70003, 1 << 19])
+def test_device_collectives_on_real_peers(registered, count):
+    """The odd count takes the per-thread paths with ragged tails; the power of two has
+    16-byte aligned blocks of at least 1 MiB, which the push kinds move by bulk copies."""
     n = min(ngpus(), 8)
     n = 8 if n >= 8 else 4 if n >= 4 else 2
-    res = run_ranks(n, "gpu_collectives", 70003, registered, timeout=300)
+    env = {"FLAGCX_BULK_COPY_MIN_BYTES": "65536"} if count % 4 == 0 else None  # default: tens of MB
+    res = run_ranks(n, "gpu_collectives", count, registered, env=env, timeout=300)
     for rank, worst in res.items():
         bad = {k: v for k, v in worst.items() if v > 1.0}
         assert not bad, (rank, bad)
