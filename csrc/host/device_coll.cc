@@ -90,6 +90,24 @@ int bulkStageFor(flagcxComm *c, const CollArgs &a) {
   return (bits & 15) ? 0 : 16384;
 }
 
+// The sum reductions at 2, 4 and 8 ranks have a variant whose inputs arrive through
+// the bulk-copy engine (Reducer::sliceBulk).  1 selects it.
+int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
+  if (a.kind != kAllReduceTwoShot && a.kind != kReduceScatter) return 0;
+  const int n = c->nranks;
+  if (a.redOp != kOpSum || (n != 2 && n != 4 && n != 8)) return 0;
+  if (a.dtype != flagcxFloat32 && a.dtype != flagcxBfloat16 && a.dtype != flagcxFloat16) return 0;
+  static const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 48 << 20);
+  const size_t es = (size_t)a.elemSize, bytes = a.count * es;
+  if (!enable || bytes % 16) return 0;
+  const size_t slice = a.kind == kReduceScatter ? a.count : sliceElems(a.count, n, es);
+  if (slice * es * (size_t)(n - 1) < (size_t)minBytes) return 0;
+  if (a.outMode == kOutBf16 && slice % 8) return 0; // output slices must start on 16 bytes too
+  uintptr_t bits = (uintptr_t)a.residual | (a.kind == kReduceScatter ? a.inStride : 0);
+  for (int p = 0; p < n; ++p) bits |= (uintptr_t)a.in[p] | (uintptr_t)a.out[p];
+  return (bits & 15) ? 0 : 1;
+}
+
 flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, cudaStream_t stream) {
   nCtas = std::max(1, std::min(nCtas, FLAGCX_COLL_BARRIER_SLOTS));
   if (c->emu) return emuSubmit(c, family, &a, nullptr, nCtas, stream);
@@ -103,8 +121,12 @@ flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, c
     b.bulkStage = bulkStageFor(c, a);
     b.bulkDepth = readParam("BULK_STAGES", 8) >= 12 ? 12 : 8;
     e = launchCopyKernel(lc, b);
+  } else if (family == kFamReduce) {
+    CollArgs b = a;
+    b.bulkStage = bulkReduceFor(c, a);
+    e = launchReduceKernel(lc, b, c->nranks);
   } else {
-    e = family == kFamReduce ? launchReduceKernel(lc, a, c->nranks) : launchNvlsKernel(lc, a);
+    e = launchNvlsKernel(lc, a);
   }
   if (e != cudaSuccess) {
     FCX_WARN("kernel launch failed: %s", cudaGetErrorString(e));

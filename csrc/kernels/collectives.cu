@@ -60,6 +60,36 @@ __device__ __forceinline__ void copyOut(const CollArgs &a, int rank, int b, int 
 }
 
 // ---------------------------------------------------------------------------
+// shared-memory ring of the bulk-copy paths (dynamic shared memory of the launch)
+// ---------------------------------------------------------------------------
+constexpr int kBulkMaxStages = 12;
+constexpr size_t kBulkRingBytes = 192u << 10;
+extern __shared__ __align__(128) unsigned char bulkRing[];
+
+__device__ __forceinline__ uint32_t smem32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Waits for the given phase parity of an mbarrier; gives up when `*abortS` is raised
+// or the communicator's time limit passes (then raises it).
+__device__ __forceinline__ bool mbarWaitBounded(const flagcxDevComm &c, uint64_t *bar, uint32_t parity,
+                                                volatile int *abortS) {
+  const uint32_t addr = smem32(bar);
+  unsigned long long t0 = 0;
+  for (unsigned spins = 0;; ++spins) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (done) return true;
+    if ((spins & 255u) == 255u) {
+      if (*abortS) return false;
+      if (t0 == 0) t0 = fcxdev::globalTimerNs();
+      else if (fcxdev::globalTimerNs() - t0 > c.timeoutNs) { *abortS = 1; return false; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // reduce family
 // ---------------------------------------------------------------------------
 template <typename T, int OP, int NR>
@@ -220,6 +250,89 @@ struct Reducer {
       storeOne(a, dst, nDst, dstBase + e, acc);
     }
   }
+
+  // The same reduction with the inputs brought in by the bulk-copy engine: one thread
+  // asks for a piece (16 bytes per thread) of every rank's input at once, peers
+  // included, into one stage of the shared-memory ring; all threads then reduce
+  // out of shared memory.  Needs NR > 0, 16-byte aligned inputs and whole packs.
+  // Loads are plain bulk copies: none is multicast.  Returns false after a timeout.
+  static __device__ bool sliceBulk(const flagcxDevComm &c, const CollArgs &a, size_t sb, size_t se, char *const *dst,
+                                   int nDst, size_t dstBase, int b, int g) {
+    constexpr int R = NR > 0 ? NR : 1;
+    __shared__ __align__(8) uint64_t full[kBulkMaxStages], empty[kBulkMaxStages];
+    __shared__ int abortS;
+    const int nt = blockDim.x, tid = threadIdx.x;
+    const uint32_t pieceBytes = (uint32_t)nt * 16u, stageBytes = pieceBytes * R;
+    int stages = (int)(kBulkRingBytes / stageBytes);
+    if (stages > kBulkMaxStages) stages = kBulkMaxStages;
+    const int ahead = stages - 1;
+    size_t ub, ue;
+    ctaShare((se - sb) * sizeof(T) >> 4, b, g, &ub, &ue);
+    const size_t nPieces = (ue - ub + nt - 1) / nt;
+    const uint32_t ring = smem32(bulkRing);
+    if (tid == 0) {
+      abortS = 0;
+      for (int s = 0; s < stages; ++s) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem32(&full[s])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem32(&empty[s])), "r"(nt >> 5) : "memory");
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async;" ::: "memory"); // a copy-in by this CTA's threads precedes the engine's reads
+    __syncthreads();
+
+    auto issue = [&](size_t j) {
+      const int s = (int)(j % stages);
+      const size_t first = ub + j * nt;
+      const uint32_t sz = (uint32_t)((ue - first) < (size_t)nt ? (ue - first) : (size_t)nt) * 16u;
+      const uint32_t bar = smem32(&full[s]);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(sz * R) : "memory");
+      for (int k = 0; k < R; ++k) {
+        int p = c.rank + 1 + k; // peers first, each rank starting with a different one
+        if (p >= R) p -= R;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         ring + s * stageBytes + p * pieceBytes),
+                     "l"(a.in[p] + sb * sizeof(T) + (first << 4)), "r"(sz), "r"(bar)
+                     : "memory");
+      }
+    };
+
+    if (tid == 0)
+      for (size_t j = 0; j < nPieces && j < (size_t)ahead; ++j) issue(j);
+    bool ok = true;
+    for (size_t i = 0; i < nPieces; ++i) {
+      if (tid == 0 && i + ahead < nPieces) {
+        const size_t j = i + ahead;
+        if (j >= (size_t)stages) ok = mbarWaitBounded(c, &empty[j % stages], (uint32_t)(j / stages - 1) & 1u, &abortS);
+        if (ok) issue(j);
+      }
+      const int s = (int)(i % stages);
+      if (ok) ok = mbarWaitBounded(c, &full[s], (uint32_t)(i / stages) & 1u, &abortS);
+      if (!ok) break;
+      const size_t pack = ub + i * nt + tid;
+      if (pack < ue) {
+        const uint4 *stage = (const uint4 *)(bulkRing + (size_t)s * stageBytes);
+        uint4 v[R];
+#pragma unroll
+        for (int p = 0; p < R; ++p) v[p] = stage[p * nt + tid];
+        Acc acc[N];
+        const T *e0 = (const T *)&v[0];
+#pragma unroll
+        for (int i2 = 0; i2 < N; ++i2) acc[i2] = toAcc<T>(e0[i2]);
+#pragma unroll
+        for (int p = 1; p < R; ++p) {
+          const T *ep = (const T *)&v[p];
+#pragma unroll
+          for (int i2 = 0; i2 < N; ++i2) acc[i2] = combine<OP, Acc>(acc[i2], toAcc<T>(ep[i2]), a.redOp);
+        }
+        storePack(a, dst, nDst, dstBase + pack * N, acc);
+      }
+      __syncwarp();
+      if ((tid & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem32(&empty[s])) : "memory");
+    }
+    if (!ok && tid == 0) fcxdev::reportError(c.status, FLAGCX_DEV_TIMEOUT, FLAGCX_DEV_AT_KERNEL, (unsigned)b, 0);
+    return !__syncthreads_or(ok ? 0 : 1);
+  }
 };
 
 template <typename T, int OP, int NR>
@@ -240,12 +353,20 @@ __device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
       size_t s = sliceElems(a.count, n, sizeof(T));
       size_t sb = s * rank < a.count ? s * rank : a.count;
       size_t se = sb + s < a.count ? sb + s : a.count;
-      R::slice(a, n, sb, se, a.out, n, sb, b, g);
+      if (NR > 0 && a.bulkStage) {
+        if (!R::sliceBulk(c, a, sb, se, a.out, n, sb, b, g)) return;
+      } else {
+        R::slice(a, n, sb, se, a.out, n, sb, b, g);
+      }
       break;
     }
     case kReduceScatter: {
       size_t sb = a.inStride / sizeof(T) * rank;
-      R::slice(a, n, sb, sb + a.count, local, 1, 0, b, g);
+      if (NR > 0 && a.bulkStage) {
+        if (!R::sliceBulk(c, a, sb, sb + a.count, local, 1, 0, b, g)) return;
+      } else {
+        R::slice(a, n, sb, sb + a.count, local, 1, 0, b, g);
+      }
       break;
     }
     case kReduceToRoot:
@@ -314,10 +435,6 @@ __device__ void ctaFanOut(char *const *dst, int nDst, const char *src, size_t by
 // half a ring ahead of the stores; a stage is reloaded only after the stores
 // that read it have left shared memory (wait_group.read).  No load here names a
 // peer and none is multicast; sources, destinations and sizes are multiples of 16.
-constexpr int kBulkMaxStages = 12; // the ring has 8 or 12 stages; the loads run half a ring ahead
-extern __shared__ __align__(128) unsigned char bulkRing[];
-
-__device__ __forceinline__ uint32_t smem32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // K destinations; sameSrc: every piece of src[0] goes to all of them (all-gather,
 // broadcast), else piece i of src[k] goes to dst[k] (all-to-all), peers interleaved.
@@ -780,7 +897,17 @@ cudaError_t launchReduceT(const LaunchCtx &lc, const CollArgs &a) {
     void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
     return cudaLaunchCooperativeKernel((const void *)reduceKernelEmu<T, OP, NR>, grid, block, params, 0, lc.stream);
   }
-  reduceKernel<T, OP, NR><<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  size_t smem = 0;
+  if (NR > 0 && a.bulkStage) {
+    smem = kBulkRingBytes;
+    static bool configured = false; // one per instantiation
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(reduceKernel<T, OP, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+  }
+  reduceKernel<T, OP, NR><<<grid, block, smem, lc.stream>>>(*lc.comm, a);
   return cudaGetLastError();
 }
 
@@ -825,7 +952,7 @@ cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a) {
   }
   size_t smem = 0;
   if (a.bulkStage) {
-    smem = (size_t)a.bulkStage * kBulkMaxStages;
+    smem = kBulkRingBytes;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(copyKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
