@@ -82,7 +82,7 @@ int bulkStageFor(flagcxComm *c, const CollArgs &a) {
   if (a.kind != kAllGatherPush && a.kind != kAllToAllPush && a.kind != kBroadcastPush) return 0;
   // measured on B200 pairs: the engine wins (about 670 against 590 GB/s per direction)
   // once a rank sends some tens of MB; below that its start-up costs more than it saves
-  static const int64_t enable = readParam("BULK_COPY", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 48 << 20);
+  static const int64_t enable = readParam("BULK_COPY", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20);
   const size_t blk = a.count * (size_t)a.elemSize;
   if (!enable || blk * (size_t)std::max(1, c->nranks - 1) < (size_t)minBytes || blk % 16) return 0;
   uintptr_t bits = (uintptr_t)a.in[c->rank] | a.inStride | a.outStride;
@@ -97,11 +97,14 @@ int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
   const int n = c->nranks;
   if (a.redOp != kOpSum || (n != 2 && n != 4 && n != 8)) return 0;
   if (a.dtype != flagcxFloat32 && a.dtype != flagcxBfloat16 && a.dtype != flagcxFloat16) return 0;
-  static const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 48 << 20);
+  // measured on 8 B200s: reduce-scatter gains from 64 MB of peer input on (667 against 606 GB/s
+  // at 4 GiB), the two-shot all-reduce only from about 400 MB on
+  static const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20),
+                       minAllReduce = readParam("BULK_ALLREDUCE_MIN_BYTES", 400 << 20);
   const size_t es = (size_t)a.elemSize, bytes = a.count * es;
   if (!enable || bytes % 16) return 0;
   const size_t slice = a.kind == kReduceScatter ? a.count : sliceElems(a.count, n, es);
-  if (slice * es * (size_t)(n - 1) < (size_t)minBytes) return 0;
+  if (slice * es * (size_t)(n - 1) < (size_t)(a.kind == kAllReduceTwoShot ? std::max(minBytes, minAllReduce) : minBytes)) return 0;
   if (a.outMode == kOutBf16 && slice % 8) return 0; // output slices must start on 16 bytes too
   uintptr_t bits = (uintptr_t)a.residual | (a.kind == kReduceScatter ? a.inStride : 0);
   for (int p = 0; p < n; ++p) bits |= (uintptr_t)a.in[p] | (uintptr_t)a.out[p];

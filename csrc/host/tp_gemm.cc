@@ -11,8 +11,8 @@
 
 namespace fcx {
 size_t tpGemmSmemBytes(bool pair);
-cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const flagcxDevComm &c,
-                         const TpGemmArgs &a, int nCtas, bool pair);
+cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const TpStoreMaps *maps,
+                         const flagcxDevComm &c, const TpGemmArgs &a, int nCtas, bool pair);
 } // namespace fcx
 
 using namespace fcx;
@@ -25,6 +25,7 @@ struct flagcxTpGemm {
   bool vmmBuf = false, vmmFlags = false;
   unsigned long long epoch = 0;
   CUtensorMap tmGather;
+  TpStoreMaps storeMaps;
   std::map<const void *, CUtensorMap> mapsA, mapsB;
 };
 
@@ -111,7 +112,7 @@ flagcxResult_t flagcxGemmBf16(const void *A, const void *B, void *D, int M, int 
   a.groupRows = groupRows(pair);
   int tiles = (M / 128) * (N / 256);
   if (pair) tiles = 2 * ((M / 256) * (N / 256));
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, ta, tb, c, a, std::min(tiles, smCount()), pair);
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, ta, tb, nullptr, c, a, std::min(tiles, smCount()), pair);
   if (e != cudaSuccess) { FCX_WARN("GEMM launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }
@@ -130,13 +131,16 @@ flagcxResult_t flagcxTpGemmCreate(flagcxComm_t comm, int mode, int M, int N, int
   h->rowsPerRank = M / n;
   const int chunks = h->rowsPerRank / 128;
   size_t bufBytes = mode == kAllGatherGemm ? (size_t)M * K * 2 : (size_t)M * N * 2;
-  size_t flagBytes = alignUp(sizeof(uint64_t) * (size_t)n * chunks, 4096);
+  size_t flagBytes = alignUp(128 * (size_t)n * chunks, 4096); // one counter per 128-byte line
   flagcxResult_t r = symAlloc(comm, bufBytes, &h->buf, &h->wBuf, &h->vmmBuf);
   if (r == flagcxSuccess) r = symAlloc(comm, flagBytes, &h->flags, &h->wFlags, &h->vmmFlags);
   if (r != flagcxSuccess) { delete h; return r; }
   FCX_CUDACHECK(cudaMemset(h->flags, 0, flagBytes));
   FCX_CUDACHECK(cudaDeviceSynchronize());
   if (mode == kAllGatherGemm) FCXCHECK(cu::tensorMap2dBf16(&h->tmGather, h->buf, M, K, 128, 64));
+  memset(&h->storeMaps, 0, sizeof h->storeMaps);
+  if (mode == kGemmReduceScatter)
+    for (int p = 0; p < n; ++p) FCXCHECK(cu::tensorMap2dBf16(&h->storeMaps.m[p], h->wBuf->peer[p], M, N, 32, 64));
   FCXCHECK(comm->bootstrap->barrier()); // flags are zero everywhere before anyone raises one
   *out = h;
   return flagcxSuccess;
@@ -179,11 +183,8 @@ flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t h, const void *B, void *D, f
     a.chunkFlags[p] = (unsigned long long *)h->wFlags->peer[p];
   }
   const int sms = smCount();
-  // a chunk is 128 rows = (K/64) x 16 KiB; pieces of at most 64 KiB that divide it evenly
-  int units = h->K / 64, per = 4;
-  while (units % per) --per;
-  a.piecesPerChunk = units / per;
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, h->tmGather, *tb, c->dev, a, sms, pair);
+  a.piecesPerChunk = h->K / 16; // a chunk is 128 rows of K bf16 = K/16 pieces of 4 KiB
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, h->tmGather, *tb, nullptr, c->dev, a, sms, pair);
   if (e != cudaSuccess) { FCX_WARN("all-gather GEMM launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }
@@ -209,7 +210,7 @@ flagcxResult_t flagcxTpGemmReduceScatter(flagcxTpGemm_t h, const void *A, const 
     a.partial[p] = (__nv_bfloat16 *)h->wBuf->peer[p];
     a.rowFlags[p] = (unsigned long long *)h->wFlags->peer[p];
   }
-  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, *ta, *tb, c->dev, a, smCount(), pair);
+  cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, *ta, *tb, &h->storeMaps, c->dev, a, smCount(), pair);
   if (e != cudaSuccess) { FCX_WARN("GEMM reduce-scatter launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }

@@ -4,18 +4,20 @@
 //
 //   mode kPlain           D[M,N] = A[M,K] * B[N,K]^T
 //   mode kAllGatherGemm   column-parallel layer: A is sequence-sharded over the ranks.
-//                         Two spare warps of EVERY CTA push this rank's shard, 64 KiB
-//                         at a time, into every peer's gather buffer over NVLink and
-//                         count each piece in on the destination; the GEMM starts with
+//                         One thread of EVERY CTA drives the bulk-copy engine: 4 KiB
+//                         pieces of this rank's shard pass through a small shared-memory
+//                         ring into every peer's gather buffer over NVLink and are
+//                         counted in on the destination; the GEMM starts with
 //                         the local rows and takes up a remote 128-row block as soon as
 //                         all of its pieces are counted in, loading it by TMA from LOCAL
 //                         memory (no TMA ever reads a peer, no multicast).
 //   mode kGemmReduceScatter  row-parallel layer: every output tile is a partial sum.
-//                         The epilogue converts the accumulator tile, transposes it
-//                         through shared memory so that every store instruction writes
-//                         whole 128-byte lines, and stores it straight into the owning
-//                         rank's partial buffer (remote owners first) and counts it in
-//                         on that rank.  A rank's own rows come last: their epilogue
+//                         The epilogue converts the accumulator tile into a swizzled
+//                         shared-memory staging and sends it by TMA tile stores straight
+//                         into the owning rank's partial buffer (remote owners first),
+//                         then counts it in on that rank.  (Per-thread stores to a peer
+//                         ran at a fifth of the link rate with the few threads an
+//                         epilogue has.)  A rank's own rows come last: their epilogue
 //                         waits for the peers' counts, adds the peers' partial tiles
 //                         (local memory by then) in fp32 and stores the final rows --
 //                         there is no separate reduction pass.
@@ -27,7 +29,7 @@
 // accumulator rows into each CTA's TMEM -- a third less operand traffic per flop.
 //
 // One persistent CTA per SM, 256 threads: warp 0 issues TMA, warp 1 issues MMA, warps
-// 2-5 run the epilogue (one TMEM lane quarter each), warps 6-7 push (all-gather mode).
+// 2-5 run the epilogue (one TMEM lane quarter each), warp 6 pushes (all-gather mode).
 // K step 64, four (single CTA) or six (pair) shared-memory stages, two accumulator
 // buffers in TMEM so that the epilogue of one tile overlaps the main loop of the next.
 // Tiles are walked in compact groups (see tileCoords) for L2 reuse.  Every wait
@@ -54,7 +56,10 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitLimitNs = 4000000000ull; // 4 s
+constexpr int kFlagStride = 16; // counters sit one per 128-byte line (see tp_gemm_args.h)
 constexpr int kEpiCols = 64;                                // columns staged per epilogue step
+constexpr int kRing = 4, kRingAhead = 2;                    // all-gather pusher: ring stages, loads in flight
+constexpr uint32_t kPieceBytes = 4096;                      // bytes per ring stage; 4 x 4 KiB = sizeof(Smem::extra)
 
 template <bool PAIR>
 struct __align__(1024) Smem {
@@ -63,10 +68,40 @@ struct __align__(1024) Smem {
   bf16 a[STAGES][BM * BK];
   bf16 b[STAGES][BROWS * BK];
   uint4 epi[4][32 * kEpiCols * 2 / 16]; // per epilogue warp: 32 rows x 64 bf16, 16-byte chunks swizzled
-  uint64_t full[STAGES], empty[STAGES], tmemFull[2], tmemEmpty[2];
+  // reduce-scatter mode: second staging buffer of every epilogue warp (TMA stores read
+  // one while the warp fills the other); all-gather mode: the pusher's ring of pieces
+  uint4 extra[4 * 32 * kEpiCols * 2 / 16];
+  uint64_t full[STAGES], empty[STAGES], tmemFull[2], tmemEmpty[2], ringFull[kRing];
   uint32_t tmemBase;
   int abortFlag;
 };
+
+// ---- bulk-copy engine helpers (no load here names a peer, none is multicast) ----
+__device__ __forceinline__ void bulkLoad(void *smemDst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smemAddr(smemDst)),
+               "l"(gsrc), "r"(bytes), "r"(smemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulkStore(void *gdst, const void *smemSrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smemAddr(smemSrc)), "r"(bytes)
+               : "memory");
+}
+// 2D tile store through a tensor map (box 64 columns x 32 rows, 128-byte swizzle)
+__device__ __forceinline__ void tmaStore2d(const CUtensorMap *map, const void *smemSrc, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1),
+               "r"(smemAddr(smemSrc))
+               : "memory");
+}
+__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulkWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N>
+__device__ __forceinline__ void bulkWaitDone() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fenceProxyAsyncSmem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void redAddRelaxedSys(unsigned long long *p, unsigned long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 
 // Which tile the grid's i-th scheduling slot covers.  Rank by rank (remote-owned row
 // blocks rotated so that every rank starts with its own rows / with a different
@@ -89,12 +124,17 @@ __device__ __forceinline__ void tileCoords(const TpGemmArgs &a, int rank, int ti
 
 __device__ __forceinline__ bool waitFlagGe(const flagcxDevComm &c, const unsigned long long *flag,
                                            unsigned long long want, volatile int *abortFlag, unsigned peer) {
-  if (fcxdev::ldAcquireSys(flag) >= want) return true;
+  // Poll with relaxed loads and fence once at the end: a stream of acquire loads from
+  // one warp made every system-scope fence of the CTA's other warps (the pusher's,
+  // the epilogue's) take about a hundred microseconds.
+  if (fcxdev::ldRelaxedSys(flag) >= want) { fcxdev::fenceSys(); return true; }
   const unsigned long long t0 = timerNs();
-  unsigned spins = 0;
+  unsigned spins = 0, ns = 100;
   for (;;) {
-    if (fcxdev::ldAcquireSys(flag) >= want) return true;
-    __nanosleep(100);
+    if (fcxdev::ldRelaxedSys(flag) >= want) { fcxdev::fenceSys(); return true; }
+    // back off: every poll is an L2 access on the line the peers' atomics must reach
+    __nanosleep(ns);
+    if (ns < 1600) ns *= 2;
     if ((++spins & 63u) == 0) {
       if (*abortFlag) return false;
       if (timerNs() - t0 > c.timeoutNs || (c.status && fcxdev::ldVolatileU32(&c.status->abortFlag))) {
@@ -109,7 +149,7 @@ __device__ __forceinline__ bool waitFlagGe(const flagcxDevComm &c, const unsigne
 template <bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
     tpGemmKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const flagcxDevComm c, const TpGemmArgs a) {
+                 const __grid_constant__ TpStoreMaps sm, const flagcxDevComm c, const TpGemmArgs a) {
   extern __shared__ uint8_t rawSmem[];
   using SmemT = Smem<PAIR>;
   constexpr int STAGES = SmemT::STAGES;
@@ -123,6 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbarInit(&s.full[i], 1); mbarInit(&s.empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbarInit(&s.tmemFull[i], 1); mbarInit(&s.tmemEmpty[i], PAIR ? 8 : 4); }
+    for (int i = 0; i < kRing; ++i) mbarInit(&s.ringFull[i], 1);
     s.abortFlag = 0;
     mbarInitFence();
     prefetchTensorMap(&tmA);
@@ -171,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int chunks = a.rowsPerRank / BM;
           const int owner = arow / a.rowsPerRank;
           if (owner != rank) {
-            ok = waitFlagGe(c, a.chunkFlags[rank] + (size_t)owner * chunks + (arow / BM) % chunks,
+            ok = waitFlagGe(c, a.chunkFlags[rank] + kFlagStride * ((size_t)owner * chunks + (arow / BM) % chunks),
                             a.epoch * (unsigned long long)a.piecesPerChunk, abortFlag, owner);
             fenceProxyAsync(); // the rows were written by a peer's stores; TMA reads them next
             if (!ok) break;
@@ -238,10 +279,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       bf16 *dbase;
       int owner = rank;
       const bf16 *others = nullptr; // reduce-scatter, own rows: slice 0 of the partial sums of these rows
+      bool tmaOut = false;          // reduce-scatter, a peer's rows: the tile leaves by TMA stores
+      int tmaRow = 0;
       if (a.mode == kGemmReduceScatter) {
         owner = (int)(growBase / a.rowsPerRank);
         const size_t rowLocal = growBase - (size_t)owner * a.rowsPerRank;
         if (owner != rank) {
+          // Per-thread stores to a peer are limited by the stores each thread may have
+          // in flight; the copy engine is not.  Row of the owner's stacked partial buffer:
+          tmaOut = true;
+          tmaRow = rank * a.rowsPerRank + (int)rowLocal;
           dbase = a.partial[owner] + ((size_t)rank * a.rowsPerRank + rowLocal) * a.N;
         } else {
           // My own rows come last in the tile order, when the peers' partial sums of them
@@ -251,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (n > 1) {
             bool ok = true;
             if (lane == 0)
-              ok = waitFlagGe(c, a.rowFlags[rank] + rowLocal / BM,
+              ok = waitFlagGe(c, a.rowFlags[rank] + kFlagStride * (rowLocal / BM),
                               a.epoch * (unsigned long long)((n - 1) * tilesN), abortFlag, 0xffffffffu);
             if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
             others = a.partial[rank] + rowLocal * a.N + (size_t)tn * BN;
@@ -264,6 +311,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       const size_t sliceElems = (size_t)a.rowsPerRank * a.N;
 #pragma unroll 1
       for (int cb = 0; cb < BN / kEpiCols; ++cb) {
+        // TMA stores alternate between the warp's two staging buffers; a buffer is
+        // rewritten only after the engine has read its previous contents out
+        uint4 *buf = (tmaOut && (cb & 1)) ? s.extra + (warp - 2) * (32 * kEpiCols * 2 / 16) : stg;
+        if (lane == 0) {
+          if (tmaOut) bulkWaitRead<1>(); else bulkWaitRead<0>();
+        }
+        __syncwarp();
         // this thread's row, 64 fp32 columns -> 64 bf16 = eight 16-byte chunks, swizzled into the staging
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -275,7 +329,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) ob[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
 #pragma unroll
-          for (int i = 0; i < 4; ++i) stg[lane * 8 + ((h * 4 + i) ^ (lane & 7))] = o[i];
+          for (int i = 0; i < 4; ++i) buf[lane * 8 + ((h * 4 + i) ^ (lane & 7))] = o[i];
+        }
+        if (tmaOut) {
+          // the staging layout is the tensor map's 128-byte swizzle: one store moves the 32 x 64 box
+          fenceProxyAsyncSmem();
+          __syncwarp();
+          if (lane == 0) {
+            tmaStore2d(&sm.m[owner], buf, tn * BN + cb * kEpiCols, tmaRow);
+            bulkCommit();
+          }
+          continue;
         }
         __syncwarp();
         // read back transposed: one instruction stores four rows x 128 contiguous bytes
@@ -324,49 +388,73 @@ __global__ void __launch_bounds__(kThreads, 1)
         else mbarArrive(&s.tmemEmpty[acc]);
       }
       if (a.mode == kGemmReduceScatter && owner != rank) {
-        // count the tile in on its owner once all four epilogue warps have stored it
+        // count the tile in on its owner once all four epilogue warps' stores are complete
+        if (lane == 0) { bulkWaitDone<0>(); fenceProxyAsync(); }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           fcxdev::fenceSys();
           const int rbLocal = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
-          fcxdev::redAddReleaseSys(a.rowFlags[owner] + rbLocal, 1ull);
+          fcxdev::redAddReleaseSys(a.rowFlags[owner] + kFlagStride * rbLocal, 1ull);
         }
       }
       if (++acc == 2) { acc = 0; accPhase ^= 1; }
     }
-  } else if (a.mode == kAllGatherGemm && n > 1) {
-    // ---- pusher warps 6..7: my shard -> every peer, piece by piece, chunk 0 first ----
-    const int t = threadIdx.x - 192; // 0..63
-    const int chunks = a.rowsPerRank / BM;
-    const size_t chunkBytes = (size_t)BM * a.K * 2;
-    const size_t pieceBytes = chunkBytes / a.piecesPerChunk;
-    const size_t shardOff = (size_t)rank * a.rowsPerRank * a.K * 2;
-    const char *src = (const char *)a.gathered[rank] + shardOff;
-    const int itemsPerChunk = (n - 1) * a.piecesPerChunk;
-    const int items = chunks * itemsPerChunk;
-    for (int u = blockIdx.x; u < items && !*abortFlag; u += G) {
-      const int ch = u / itemsPerChunk, rem = u % itemsPerChunk;
-      const int piece = rem / (n - 1);
-      int p = rank + 1 + rem % (n - 1);
-      if (p >= n) p -= n;
-      const size_t off = ch * chunkBytes + piece * pieceBytes;
-      const uint4 *sv = (const uint4 *)(src + off);
-      uint4 *dv = (uint4 *)((char *)a.gathered[p] + shardOff + off);
-      const size_t nv = pieceBytes >> 4;
-      size_t i = t;
-      for (; i + 7 * 64 < nv; i += 8 * 64) {
-        uint4 r[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) r[k] = ldLocal16(sv + i + k * 64);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) st16(dv + i + k * 64, r[k]);
-      }
-      for (; i < nv; i += 64) st16(dv + i, ldLocal16(sv + i));
-      asm volatile("bar.sync 2, 64;" ::: "memory");
-      if (t == 0) {
+  } else if (warp == 6 && a.mode == kAllGatherGemm && n > 1) {
+    // ---- pusher: one thread drives the copy engine.  My shard goes out in 4 KiB
+    // pieces, chunk 0 first: bulk load into a ring stage, one bulk store per peer
+    // from that stage, and once a piece's stores are complete it is counted in on
+    // every peer.  The pieces of one chunk are spread over all CTAs. ----
+    if (lane == 0) {
+      const int chunks = a.rowsPerRank / BM;
+      const size_t shardBytes = (size_t)a.rowsPerRank * a.K * 2;
+      const size_t shardOff = (size_t)rank * shardBytes;
+      const char *src = (const char *)a.gathered[rank] + shardOff;
+      const long long nPieces = (long long)(shardBytes / kPieceBytes);
+      const long long cnt = blockIdx.x < nPieces ? (nPieces - blockIdx.x + G - 1) / G : 0;
+      char *ring = (char *)s.extra;
+      auto pieceOf = [&](long long i) { return (size_t)blockIdx.x + (size_t)i * G; };
+      auto issueLoad = [&](long long i) {
+        const int st = (int)(i % kRing);
+        mbarExpectTx(&s.ringFull[st], kPieceBytes);
+        bulkLoad(ring + st * kPieceBytes, src + pieceOf(i) * kPieceBytes, kPieceBytes, &s.ringFull[st]);
+      };
+      // Completed pieces are counted in on the peers once per chunk (this CTA's pieces
+      // of one chunk are consecutive): one fence and one atomic per peer and chunk.
+      long long pendChunk = -1;
+      unsigned long long pendCount = 0;
+      auto flush = [&]() {
+        if (pendCount == 0) return;
+        fenceProxyAsync();
         fcxdev::fenceSys();
-        fcxdev::redAddReleaseSys(a.chunkFlags[p] + (size_t)rank * chunks + ch, 1ull);
+        for (int k = 1; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          redAddRelaxedSys(a.chunkFlags[p] + kFlagStride * ((size_t)rank * chunks + pendChunk), pendCount);
+        }
+        pendCount = 0;
+      };
+      auto countIn = [&](long long i) {
+        const long long ch = (long long)(pieceOf(i) / a.piecesPerChunk);
+        if (ch != pendChunk) { flush(); pendChunk = ch; }
+        ++pendCount;
+      };
+      for (long long i = 0; i < cnt && i < kRingAhead; ++i) issueLoad(i);
+      long long i = 0;
+      for (; i < cnt && !*abortFlag; ++i) {
+        // stage of piece i+ahead = stage of piece i+ahead-ring, complete since the last iteration's wait
+        if (i + kRingAhead < cnt) issueLoad(i + kRingAhead);
+        const int st = (int)(i % kRing);
+        if (!mbarWait(&s.ringFull[st], (uint32_t)(i / kRing) & 1u, abortFlag, kWaitLimitNs)) break;
+        const size_t off = shardOff + pieceOf(i) * kPieceBytes;
+        for (int k = 1; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          bulkStore((char *)a.gathered[p] + off, ring + st * kPieceBytes, kPieceBytes);
+        }
+        bulkCommit();
+        if (i >= 1) { bulkWaitDone<1>(); countIn(i - 1); }
       }
+      bulkWaitDone<0>();
+      if (i == cnt && cnt > 0) countIn(cnt - 1);
+      flush();
     }
   }
 
@@ -386,8 +474,10 @@ size_t tpGemmSmemBytes(bool pair) { return (pair ? sizeof(Smem<true>) : sizeof(S
 
 // pair: use CTA pairs (cluster of two, 256 x 256 tiles); needs an even grid and M a
 // multiple of 256 (per rank in the fused modes).
-cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const flagcxDevComm &c,
-                         const TpGemmArgs &a, int nCtas, bool pair) {
+cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUtensorMap &tmB, const TpStoreMaps *maps,
+                         const flagcxDevComm &c, const TpGemmArgs &a, int nCtas, bool pair) {
+  static const TpStoreMaps noMaps = {};
+  const TpStoreMaps &sm = maps ? *maps : noMaps;
   static bool configured[2] = {false, false};
   const void *fn = pair ? (const void *)tpGemmKernel<true> : (const void *)tpGemmKernel<false>;
   if (!configured[pair]) {
@@ -396,7 +486,7 @@ cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUte
     configured[pair] = true;
   }
   if (!pair) {
-    tpGemmKernel<false><<<nCtas, kThreads, tpGemmSmemBytes(false), stream>>>(tmA, tmB, c, a);
+    tpGemmKernel<false><<<nCtas, kThreads, tpGemmSmemBytes(false), stream>>>(tmA, tmB, sm, c, a);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
@@ -411,7 +501,7 @@ cudaError_t launchTpGemm(cudaStream_t stream, const CUtensorMap &tmA, const CUte
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, tpGemmKernel<true>, tmA, tmB, c, a);
+  return cudaLaunchKernelEx(&cfg, tpGemmKernel<true>, tmA, tmB, sm, c, a);
 }
 
 } // namespace fcx
