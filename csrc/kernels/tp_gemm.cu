@@ -103,9 +103,9 @@ __device__ __forceinline__ void redAddRelaxedSys(unsigned long long *p, unsigned
   asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// Which tile the grid's i-th scheduling slot covers.  Rank by rank (remote-owned row
-// blocks rotated so that every rank starts with its own rows / with a different
-// peer's), and inside one rank's rows in groups of `groupRows` row blocks that are
+// Which tile the grid's i-th scheduling slot covers.  The row blocks are taken in an
+// order that suits the mode (below), cut into runs of one rank's worth, and inside a
+// run in groups of `groupRows` row blocks that are
 // walked column by column: the tiles in flight at any moment then form a compact
 // rectangle (about 8 x 9 tiles of 256 x 256) instead of a one-tile-high stripe, so the
 // rows of A and B that they share are fetched from HBM once and hit in L2 afterwards.
@@ -117,8 +117,19 @@ __device__ __forceinline__ void tileCoords(const TpGemmArgs &a, int rank, int ti
   const int gsize = min(a.groupRows, bpr - g * a.groupRows);
   *tn = wg / gsize;
   int rb = r * bpr + g * a.groupRows + (wg - *tn * gsize);
-  if (a.mode == kAllGatherGemm) rb = (rb + rank * bpr) % blocks;                 // own rows first
-  else if (a.mode == kGemmReduceScatter) rb = (rb + (rank + 1) * bpr) % blocks; // own rows last
+  if (a.mode == kAllGatherGemm) {
+    // own rows first; then the peers' rows in the order in which the pushers deliver
+    // them: block 0 of every peer, block 1 of every peer, ...
+    if (rb < bpr) {
+      rb += rank * bpr;
+    } else {
+      const int peers = blocks / bpr - 1, j = rb - bpr;
+      const int blk = j / peers, src = (rank + 1 + j % peers) % (peers + 1);
+      rb = src * bpr + blk;
+    }
+  } else if (a.mode == kGemmReduceScatter) {
+    rb = (rb + (rank + 1) * bpr) % blocks; // own rows last
+  }
   *tm = rb;
 }
 
