@@ -79,6 +79,19 @@ def host_collectives(rank, n, uid, count, dtype_code):
     return out
 
 
+def host_collectives_through_plugin(rank, n, uid, count, plugin_path):
+    """The host collectives with FLAGCX_NET_ADAPTOR_PLUGIN set: results as usual, and the
+    plugin's own counters show that it carried the traffic."""
+    import ctypes
+    out = host_collectives(rank, n, uid, count, capi.FLOAT)
+    plug = ctypes.CDLL(plugin_path)  # same object the library loaded
+    sent, recvd, msgs = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    plug.flagcxNetExampleCounters(ctypes.byref(sent), ctypes.byref(recvd), ctypes.byref(msgs))
+    out["plugin_bytes_sent"] = int(sent.value)
+    out["plugin_messages"] = int(msgs.value)
+    return out
+
+
 def host_all_ops(rank, n, uid, count):
     """Every collective, several dtypes and reductions, odd counts."""
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)

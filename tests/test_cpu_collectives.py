@@ -46,6 +46,23 @@ def test_multi_socket_striping_and_helper_threads():
         assert all(e <= 1e-6 for e in errs.values()), errs
 
 
+def test_net_adaptor_plugin_carries_the_host_collectives():
+    """csrc/plugin/net_example.cc, built here, replaces the socket adaptor
+    (role of adaptor_plugin/net in the FlagCX project)."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run(["make", "-C", os.path.join(root, "csrc"), "plugin-example"], check=True, capture_output=True)
+    plugin = os.path.join(root, "flagcx_b200", "lib", "libflagcx_net_example.so")
+    count = 50000
+    res = run_ranks(3, "host_collectives_through_plugin", count, plugin,
+                    env={"FLAGCX_NET_ADAPTOR_PLUGIN": plugin}, timeout=120)
+    for rank, out in res.items():
+        assert out["plugin_bytes_sent"] >= count * 4 and out["plugin_messages"] > 0, (rank, out)
+        errs = {k: v for k, v in out.items() if not k.startswith("plugin_") and v > 1e-5}
+        assert not errs, (rank, errs)
+
+
 def test_comm_id_environment_rendezvous():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
