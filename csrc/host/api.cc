@@ -136,7 +136,9 @@ flagcxResult_t flagcxGetUniqueId(flagcxUniqueId_t uniqueId) {
 flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks, flagcxUniqueId_t commId, int rank) {
   if (!comm || !commId) return flagcxInvalidArgument;
   *comm = nullptr;
-  return commCreate(comm, nranks, *commId, rank);
+  FCXCHECK(commCreate(comm, nranks, *commId, rank));
+  if (int64_t cap = readParam("TRACE", 0)) (*comm)->trace.enable((int)std::min<int64_t>(cap, 1 << 20));
+  return flagcxSuccess;
 }
 
 flagcxResult_t flagcxCommFinalize(flagcxComm_t comm) {
@@ -151,6 +153,15 @@ flagcxResult_t flagcxCommFinalize(flagcxComm_t comm) {
 
 flagcxResult_t flagcxCommDestroy(flagcxComm_t comm) {
   FCX_COMMCHECK(comm);
+  if (comm->trace.on()) {
+    if (const char *f = getEnv("FLAGCX_TRACE_FILE")) { // %r -> rank
+      std::string path(f);
+      size_t at = path.find("%r");
+      if (at != std::string::npos) path.replace(at, 2, std::to_string(comm->rank));
+      comm->trace.dump(comm, path.c_str());
+    }
+    comm->trace.enable(0); // events go before the context does
+  }
   return commDestroy(comm);
 }
 
@@ -312,6 +323,17 @@ static flagcxResult_t runCollective(flagcxComm *c, DeviceCollRequest &rq, size_t
   FCXCHECK(checkUsable(c));
   FCX_TRACE(SUB_CALL, "%s count %zu %s rank %d", commOpName(rq.op), rq.count, dtypeName(rq.dtype), c->rank);
   Route route = routeFor(c, rq.send, rq.recv);
+  // trace record and NVTX range around whatever route the call takes
+  struct Scope {
+    flagcxComm *c;
+    int slot;
+    cudaStream_t s;
+    ~Scope() { c->trace.end(c, slot, s); nvtxPop(); }
+  };
+  nvtxPush(commOpName(rq.op));
+  Scope scope{c, c->trace.begin(c, rq.op, std::max(sendBytes, recvBytes),
+                                route == kRouteDevice ? 0 : route == kRouteHost ? 1 : 2, rawStream(stream)),
+              rawStream(stream)};
   if (route == kRouteDevice) return deviceCollective(c, rq, rawStream(stream));
   auto host = [&](const void *s, void *r) -> flagcxResult_t {
     CpuColl &cc = c->cpu;
@@ -735,6 +757,19 @@ flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t byt
   if (algo) *algo = ch.algo;
   if (nCtas) *nCtas = ch.nCtas;
   return flagcxSuccess;
+}
+
+flagcxResult_t flagcxCommTraceEnable(flagcxComm_t comm, int capacity) {
+  FCX_COMMCHECK(comm);
+  if (capacity < 0 || capacity > (1 << 20)) return flagcxInvalidArgument;
+  comm->trace.enable(capacity);
+  return flagcxSuccess;
+}
+
+flagcxResult_t flagcxCommTraceDump(flagcxComm_t comm, const char *path) {
+  FCX_COMMCHECK(comm);
+  if (!comm->trace.on()) return flagcxInvalidUsage;
+  return comm->trace.dump(comm, path);
 }
 
 flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOpStats_t *out) {

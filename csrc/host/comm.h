@@ -15,6 +15,7 @@
 #include <thread>
 #include <vector>
 
+#include "trace.h"
 #include "bootstrap.h"
 #include "cpu_coll.h"
 #include "cuda_rt.h"
@@ -138,6 +139,7 @@ struct flagcxComm {
   std::atomic<int> asyncError{flagcxSuccess};
   std::string lastError;
   fcx::OpStats stats[flagcxNumCommOps];
+  fcx::Trace trace;
   std::thread watchdog;
   std::atomic<bool> watchdogStop{false};
   bool finalized = false;

@@ -71,6 +71,14 @@ typedef struct {
   float lastMs; /* device time of the last profiled call (0 when profiling is off) */
 } flagcxOpStats_t;
 flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOpStats_t *out);
+/* Trace: a ring of the last `capacity` collective calls of this communicator (operation,
+ * bytes, route, algorithm, CTAs, host time, device time between two CUDA events on the
+ * caller's stream).  capacity 0 switches it off.  FLAGCX_TRACE=<capacity> enables it at
+ * init; FLAGCX_TRACE_FILE=<path, %r = rank> writes it at flagcxCommDestroy.  Dump
+ * synchronises the recorded events, fills flagcxOpStats_t.lastMs and writes JSON.
+ * FLAGCX_NVTX=1 additionally opens an NVTX range around every collective. */
+flagcxResult_t flagcxCommTraceEnable(flagcxComm_t comm, int capacity);
+flagcxResult_t flagcxCommTraceDump(flagcxComm_t comm, const char *path);
 /* 1 when collectives on device buffers run as NVLink kernels, 0 on the socket path. */
 flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes);
 flagcxResult_t flagcxCommHasMulticast(flagcxComm_t comm, int *yes);

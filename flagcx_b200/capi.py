@@ -230,6 +230,14 @@ class Comm:
     def set_wait_timeout_ms(self, ms: int):
         check(lib().flagcxCommSetWaitTimeoutMs(self.h, ms), "flagcxCommSetWaitTimeoutMs", self.h)
 
+    def trace_enable(self, capacity: int):
+        """Keep the last `capacity` collective calls in a ring (0: off)."""
+        check(lib().flagcxCommTraceEnable(self.h, int(capacity)), "flagcxCommTraceEnable", self.h)
+
+    def trace_dump(self, path: str):
+        """Write the ring as JSON (synchronises the recorded CUDA events)."""
+        check(lib().flagcxCommTraceDump(self.h, path.encode()), "flagcxCommTraceDump", self.h)
+
     def stats(self, op: int) -> OpStats:
         s = OpStats()
         check(lib().flagcxCommGetStats(self.h, op, C.byref(s)), "flagcxCommGetStats", self.h)

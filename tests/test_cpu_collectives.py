@@ -126,3 +126,27 @@ def test_host_reduce_half_and_bfloat16_round_to_nearest_even():
     rounded = ((s + 0x7FFF + ((s >> 16) & 1)) >> 16).astype(np.uint16)
     capi.host_reduce(xb, yb, capi.BFLOAT16, capi.SUM)
     assert np.array_equal(xb, rounded)
+
+
+def test_trace_ring_records_calls_and_dumps_json(tmp_path):
+    """Role of the event-record ring behind the FlagCX tuner's Start/StopProfiling."""
+    import json
+    comm = capi.Comm.init_rank(1, capi.get_unique_id(), 0)
+    comm.trace_enable(4)
+    x = np.arange(1000, dtype=np.float32)
+    y = np.empty_like(x)
+    for _ in range(6):  # more calls than slots: the ring keeps the last four
+        comm.all_reduce(x, y, x.size, capi.FLOAT, capi.SUM)
+    comm.all_gather(x, y, x.size, capi.FLOAT)
+    path = str(tmp_path / "trace.json")
+    comm.trace_dump(path)
+    doc = json.load(open(path))
+    recs = doc["records"]
+    assert doc["rank"] == 0 and len(recs) == 4
+    assert [r["seq"] for r in recs] == [3, 4, 5, 6]
+    assert recs[-1]["op"].lower().replace("_", "") == "allgather" and recs[0]["bytes"] == 4000
+    assert all(r["route"] == "host" and r["host_us"] > 0 for r in recs)
+    comm.trace_enable(0)
+    with pytest.raises(capi.FlagcxError):
+        comm.trace_dump(path)
+    comm.destroy()
