@@ -3,6 +3,7 @@ a few hundred MB on the device at most, inputs larger than the 126 MB L2 where D
 figures matter).  Each case also prints its CUDA-event time.
 
     python bench/profile_cases.py --case gemm            # tcgen05 GEMM 8192 x 3584 x 8192
+    python bench/profile_cases.py --case gemm_large      # 8192 x 14336 x 8192 (B larger than L2; 0.6 GB on the device)
     python bench/profile_cases.py --case allreduce       # 8 emulated ranks, two-shot, 32 MiB bf16 each
     python bench/profile_cases.py --case reducescatter   # 8 emulated ranks, 8 x 8 MiB bf16 each
     python bench/profile_cases.py --case allgather       # 8 emulated ranks, push
@@ -44,9 +45,9 @@ def main():
     ap.add_argument("--case", required=True)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    if args.case == "gemm":
+    if args.case in ("gemm", "gemm_large"):
         from flagcx_b200.parallel.tp import gemm_bf16
-        M, N, K = 8192, 3584, 8192
+        M, N, K = (8192, 3584, 8192) if args.case == "gemm" else (8192, 14336, 8192)
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
         out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
