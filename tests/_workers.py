@@ -92,6 +92,48 @@ def host_collectives_through_plugin(rank, n, uid, count, plugin_path):
     return out
 
 
+def nccl_shim_program(rank, n, uid, shim_path, count):
+    """What a program written against NCCL does, through the preloadable stand-in:
+    init from a 128-byte id, all-reduce, all-gather, a grouped ring send/recv."""
+    import ctypes as C
+
+    class NcclUniqueId(C.Structure):
+        _fields_ = [("internal", C.c_char * 128)]
+
+    capi.lib()  # libflagcx.so resident (the shim links against it)
+    nccl = C.CDLL(shim_path)
+    nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, NcclUniqueId, C.c_int]
+    nccl.ncclGetErrorString.restype = C.c_char_p
+    nid = NcclUniqueId()
+    C.memmove(C.byref(nid), uid[:128], 128)  # (a c_char array field reads back as a copy)
+    assert not any(uid[128:]), "the bootstrap id must fit NCCL's 128 bytes"
+    comm = C.c_void_p()
+    rc = nccl.ncclCommInitRank(C.byref(comm), n, nid, rank)
+    assert rc == 0, nccl.ncclGetErrorString(rc)
+    got_rank, got_n = C.c_int(-1), C.c_int(-1)
+    assert nccl.ncclCommUserRank(comm, C.byref(got_rank)) == 0 and nccl.ncclCommCount(comm, C.byref(got_n)) == 0
+    assert (got_rank.value, got_n.value) == (rank, n)
+    NCCL_FLOAT, NCCL_SUM = 7, 0
+    xs = [seeded(r, count, capi.FLOAT) for r in range(n)]
+    x, out = xs[rank], {}
+    ar = np.empty_like(x)
+    p = lambda a: C.c_void_p(a.ctypes.data)  # noqa: E731
+    assert nccl.ncclAllReduce(p(x), p(ar), C.c_size_t(count), NCCL_FLOAT, NCCL_SUM, comm, None) == 0
+    out["allreduce"] = rel_err(ar, np_reduce(xs, capi.SUM))
+    ag = np.empty(count * n, np.float32)
+    assert nccl.ncclAllGather(p(x), p(ag), C.c_size_t(count), NCCL_FLOAT, comm, None) == 0
+    out["allgather"] = float(not np.array_equal(ag, np.concatenate(xs)))
+    got = np.empty_like(x)
+    assert nccl.ncclGroupStart() == 0
+    assert nccl.ncclSend(p(x), C.c_size_t(count), NCCL_FLOAT, (rank + 1) % n, comm, None) == 0
+    assert nccl.ncclRecv(p(got), C.c_size_t(count), NCCL_FLOAT, (rank - 1) % n, comm, None) == 0
+    assert nccl.ncclGroupEnd() == 0
+    out["sendrecv"] = float(not np.array_equal(got, xs[(rank - 1) % n]))
+    assert nccl.ncclAllReduce(p(x), p(ar), C.c_size_t(count), 11, NCCL_SUM, comm, None) == 4  # fp8: invalid argument
+    assert nccl.ncclCommDestroy(comm) == 0
+    return out
+
+
 def host_all_ops(rank, n, uid, count):
     """Every collective, several dtypes and reductions, odd counts."""
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)

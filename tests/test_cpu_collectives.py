@@ -150,3 +150,23 @@ def test_trace_ring_records_calls_and_dumps_json(tmp_path):
     with pytest.raises(capi.FlagcxError):
         comm.trace_dump(path)
     comm.destroy()
+
+
+def test_nccl_stand_in_runs_an_nccl_program_on_this_library():
+    """csrc/shim/nccl_shim.cc (role of plugin/nccl in the FlagCX project)."""
+    import ctypes
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run(["make", "-C", os.path.join(root, "csrc"), "nccl-shim"], check=True, capture_output=True)
+    shim = os.path.join(root, "flagcx_b200", "lib", "libnccl_flagcx_shim.so")
+    capi.lib()
+    nccl = ctypes.CDLL(shim)
+    v = ctypes.c_int()
+    assert nccl.ncclGetVersion(ctypes.byref(v)) == 0 and v.value >= 22000
+    uid = (ctypes.c_char * 128)()
+    assert nccl.ncclGetUniqueId(uid) == 0 and any(bytes(uid))
+    assert nccl.ncclCommInitAll(None, 2, None) == 5  # one process per GPU: invalid usage
+    res = run_ranks(3, "nccl_shim_program", shim, 30000, timeout=120)
+    for rank, out in res.items():
+        assert all(v < 1e-5 for v in out.values()), (rank, out)
