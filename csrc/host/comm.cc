@@ -343,6 +343,20 @@ static flagcxResult_t setupDeviceWorld(flagcxComm *c, const std::vector<PeerInfo
 
 flagcxResult_t commCreate(flagcxComm **out, int nranks, const flagcxUniqueId &id, int rank) {
   logInit();
+  // Settings of the FlagCX project that select machinery this library does not have:
+  // say so once instead of ignoring them silently.
+  static const bool warned = [] {
+    static const char *const unsupported[] = {
+        "FLAGCX_CLUSTER_SPLIT_LIST",    // heterogeneous cluster planner
+        "FLAGCX_CCL_ADAPTOR_PLUGIN",    // vendor collective-library plugins
+        "FLAGCX_DEVICE_ADAPTOR_PLUGIN", // vendor device-runtime plugins
+        "FLAGCX_TOPO_FILE",             // PCI/NIC topology XML
+        "FLAGCX_INTERSERVER_ROUTE_FILE"};
+    for (const char *name : unsupported)
+      if (getEnv(name)) FCX_WARN("%s is set but has no effect: single-vendor NVLink library (see docs/environment_variables.md)", name);
+    return true;
+  }();
+  (void)warned;
   auto c = std::make_unique<flagcxComm>();
   c->magic = kCommMagic;
   c->rank = rank;
