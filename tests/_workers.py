@@ -561,3 +561,48 @@ def torch_ddp_parity(rank, n, uid_unused, port, backend, use_cuda):
         losses.append(float(t) / n)
     dist.destroy_process_group()
     return losses
+
+
+# ---------------------------------------------------------------------------
+# pipeline parallelism
+# ---------------------------------------------------------------------------
+def _pp_stage_module(stage, width):
+    import torch
+    g = torch.Generator().manual_seed(100 + stage)
+    lin = torch.nn.Linear(width, width)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(width, width, generator=g) * 0.3)
+        lin.bias.copy_(torch.randn(width, generator=g) * 0.1)
+    return torch.nn.Sequential(lin, torch.nn.Tanh())
+
+
+def pp_1f1b(rank, n, uid, n_micro, width):
+    """1F1B over n stages on CPU tensors against the same model run in one process."""
+    import torch
+    from flagcx_b200.parallel.pp import PipelineStage
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    batch = 4
+    g = torch.Generator().manual_seed(7)
+    xs = [torch.randn(batch, width, generator=g) for _ in range(n_micro)]
+    ts = [torch.randn(batch, width, generator=g) for _ in range(n_micro)]
+    stage = PipelineStage(comm, _pp_stage_module(rank, width), None if rank == 0 else (batch, width), (batch, width))
+    loss = stage.run_1f1b(xs if rank == 0 else None, n_micro,
+                          (lambda y, i: ((y - ts[i]) ** 2).mean() / n_micro) if rank == n - 1 else None)
+    # reference: the whole model here
+    full = [_pp_stage_module(s, width) for s in range(n)]
+    ref_loss = 0.0
+    for i in range(n_micro):
+        y = xs[i]
+        for m in full:
+            y = m(y)
+        l = ((y - ts[i]) ** 2).mean() / n_micro
+        l.backward()
+        ref_loss += float(l)
+    mine, ref = stage.module[0], full[rank][0]
+    out = {"grad_w": float((mine.weight.grad - ref.weight.grad).abs().max()),
+           "grad_b": float((mine.bias.grad - ref.bias.grad).abs().max())}
+    if rank == n - 1:
+        out["loss"] = abs(loss - ref_loss)
+    comm.barrier()
+    comm.destroy()
+    return out
