@@ -69,7 +69,9 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       break;
   }
   (void)registered;
-  size_t perCta = 16u << 10;
+  // work per CTA below which another CTA costs more (its barrier flags on every peer)
+  // than it brings; the offline tuner on B200 pairs picked 8 CTAs for 1-2 MiB
+  static const size_t perCta = (size_t)std::max<int64_t>(1024, readParam("BYTES_PER_CTA", 64 << 10));
   // bandwidth-bound sizes get twice the CTAs: more NVLink accesses in flight
   size_t cap = work >= (16u << 20) ? std::min<size_t>(2 * (size_t)maxCtas, FLAGCX_COLL_BARRIER_SLOTS) : (size_t)maxCtas;
   ch.nCtas = (int)std::max<size_t>(1, std::min<size_t>((work + perCta - 1) / perCta, cap));
