@@ -170,3 +170,21 @@ def test_nccl_stand_in_runs_an_nccl_program_on_this_library():
     res = run_ranks(3, "nccl_shim_program", shim, 30000, timeout=120)
     for rank, out in res.items():
         assert all(v < 1e-5 for v in out.values()), (rank, out)
+
+
+def test_c_api_example_program_forks_its_ranks_and_checks_results():
+    """csrc/examples/allreduce_perf.cc uses only flagcx.h (device handle table, streams,
+    events, collectives); role of test/perf/host_api/test_allreduce.cpp in the FlagCX project."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run(["make", "-C", os.path.join(root, "csrc"), "examples"], check=True, capture_output=True)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    exe = os.path.join(root, "csrc", "build", "examples", "allreduce_perf")
+    env = {k: v for k, v in os.environ.items() if k != "FLAGCX_COMM_ID"}
+    res = subprocess.run([exe, "-n", "3", "--host", "-b", "1K", "-e", "256K", "-f", "4", "-w", "1", "-i", "2", "-p", str(port)],
+                         capture_output=True, text=True, timeout=120, env=env)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.count(" ok") == 5 and "WRONG" not in res.stdout, res.stdout
