@@ -606,3 +606,43 @@ def pp_1f1b(rank, n, uid, n_micro, width):
     comm.barrier()
     comm.destroy()
     return out
+
+
+def host_random_stress(rank, n, uid, rounds, seed):
+    """Random operations, sizes and per-rank delays on the host path: every rank draws the
+    same schedule from `seed` and its own sleeps from (seed, rank)."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    plan = np.random.default_rng(seed)
+    jitter = np.random.default_rng(seed * 1000 + rank)
+    worst = 0.0
+    for it in range(rounds):
+        op = int(plan.integers(0, 5))
+        count = int(plan.integers(1, 40000))
+        root = int(plan.integers(0, n))
+        xs = [np.random.default_rng(seed + 17 * it + r).uniform(-1, 1, count * n).astype(np.float32) for r in range(n)]
+        x = xs[rank]
+        time.sleep(float(jitter.uniform(0, 0.004)))
+        if op == 0:
+            out = np.empty_like(x)
+            comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+            worst = max(worst, rel_err(out, np_reduce(xs, capi.SUM)))
+        elif op == 1:
+            out = np.empty(count * n, np.float32)
+            comm.all_gather(x[:count], out, count, capi.FLOAT)
+            worst = max(worst, float(not np.array_equal(out, np.concatenate([a[:count] for a in xs]))))
+        elif op == 2:
+            out = np.empty(count, np.float32)
+            comm.reduce_scatter(x, out, count, capi.FLOAT, capi.SUM)
+            worst = max(worst, rel_err(out, np_reduce(xs, capi.SUM)[rank * count:(rank + 1) * count]))
+        elif op == 3:
+            out = np.empty(count * n, np.float32)
+            comm.all_to_all(x, out, count, capi.FLOAT)
+            want = np.concatenate([xs[p][rank * count:(rank + 1) * count] for p in range(n)])
+            worst = max(worst, float(not np.array_equal(out, want)))
+        else:
+            buf = x[:count].copy()
+            comm.broadcast(buf, buf, count, capi.FLOAT, root)
+            worst = max(worst, float(not np.array_equal(buf, xs[root][:count])))
+    comm.barrier()
+    comm.destroy()
+    return worst

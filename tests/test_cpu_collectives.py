@@ -188,3 +188,11 @@ def test_c_api_example_program_forks_its_ranks_and_checks_results():
                          capture_output=True, text=True, timeout=120, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
     assert res.stdout.count(" ok") == 5 and "WRONG" not in res.stdout, res.stdout
+
+
+@pytest.mark.parametrize("n,seed", [(2, 1), (4, 2), (5, 3)])
+def test_random_schedule_with_per_rank_delays(n, seed):
+    """Back-to-back collectives of random kind and size while the ranks drift apart by
+    random sleeps: connections, tags and buffers must never get mixed up."""
+    res = run_ranks(n, "host_random_stress", 40, seed, timeout=180)
+    assert all(v < 1e-5 for v in res.values()), res
