@@ -171,7 +171,7 @@ void logWrite(LogLevel lvl, uint32_t subsys, const char *file, int line,
   va_start(ap, fmt);
   vsnprintf(body, sizeof body, fmt, ap);
   va_end(ap);
-  if (lvl == LOG_WARN) snprintf(tlsLastError, sizeof tlsLastError, "%s", body);
+  if (lvl == LOG_WARN) snprintf(tlsLastError, sizeof tlsLastError, "%.*s", (int)sizeof tlsLastError - 1, body);
   int cur = logLevel();
   if (cur < (int)lvl) return;
   if (lvl != LOG_WARN && !(subsys & gSubsys)) return;
