@@ -2,6 +2,8 @@
 #include "cpu_coll.h"
 
 #include <sched.h>
+#include <string.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <cmath>
@@ -163,10 +165,70 @@ flagcxResult_t HostNet::init(Bootstrap *bs) {
   FCXCHECK(bs->allGather(handles_.data(), FLAGCX_NET_HANDLE_BYTES));
   send_.assign(n, nullptr);
   recv_.assign(n, nullptr);
+  return initShm();
+}
+
+// Every rank creates one ring towards each rank of its own machine; shared memory is
+// used only if ALL ranks got ALL their rings (otherwise everybody closes them again and
+// the adaptor carries everything), so the two ends of a pair never disagree.
+flagcxResult_t HostNet::initShm() {
+  const int n = bs_->nranks(), me = bs_->rank();
+  shmSend_.clear();
+  shmRecv_.clear();
+  shmSend_.resize(n);
+  shmRecv_.resize(n);
+  struct Info {
+    uint64_t host;
+    int32_t pid;
+    int32_t ok;
+  };
+  std::vector<Info> infos(n);
+  infos[me] = {hostHash(), (int32_t)getpid(), 0};
+  const bool want = n > 1 && readParam("HOST_SHM", 1) != 0 && !strcmp(net_->name, "socket");
+  FCXCHECK(bs_->allGather(infos.data(), sizeof(Info)));
+  size_t cap = (size_t)std::max<int64_t>(4096, readParam("SHM_RING_BYTES", 1 << 20));
+  while (cap & (cap - 1)) cap &= cap - 1; // round down to a power of two
+  auto nameOf = [&](int src, int dst) {
+    char b[96];
+    snprintf(b, sizeof b, "/flagcx-%016llx-%d-%d", (unsigned long long)bs_->nonce(), src, dst);
+    return std::string(b);
+  };
+  bool ok = want;
+  if (want) {
+    for (int p = 0; p < n && ok; ++p) {
+      if (p == me || infos[p].host != infos[me].host) continue;
+      shmSend_[p].reset(new ShmRing());
+      ok = shmSend_[p]->create(nameOf(me, p), cap) == flagcxSuccess;
+    }
+  }
+  infos[me].ok = ok ? 1 : 0;
+  FCXCHECK(bs_->allGather(infos.data(), sizeof(Info))); // also: every ring exists from here on
+  bool all = true;
+  for (int p = 0; p < n; ++p) all = all && infos[p].ok;
+  pids_.assign(n, 0);
+  for (int p = 0; p < n; ++p) pids_[p] = infos[p].pid;
+  if (all) {
+    for (int p = 0; p < n && all; ++p) {
+      if (p == me || infos[p].host != infos[me].host) continue;
+      shmRecv_[p].reset(new ShmRing());
+      all = shmRecv_[p]->open(nameOf(p, me)) == flagcxSuccess;
+    }
+    if (!all) { FCX_WARN("host shm: a ring that its creator announced could not be opened"); return flagcxSystemError; }
+  }
+  if (!all) {
+    for (auto &r : shmSend_) r.reset();
+    for (auto &r : shmRecv_) r.reset();
+  }
+  shm_ = all;
+  FCXCHECK(bs_->barrier()); // nobody writes before every receiver is attached and the names are gone
+  if (want) FCX_INFO(SUB_SHM, "rank %d: host shared-memory rings %s (%zu KiB each)", me, shm_ ? "on" : "off", cap >> 10);
   return flagcxSuccess;
 }
 
 void HostNet::close() {
+  shmSend_.clear();
+  shmRecv_.clear();
+  shm_ = false;
   if (!net_) return;
   for (void *&c : send_) if (c) { net_->closeSend(c); c = nullptr; }
   for (void *&c : recv_) if (c) { net_->closeRecv(c); c = nullptr; }
@@ -226,12 +288,25 @@ flagcxResult_t HostNet::run(const std::vector<Op> &ops) {
   std::vector<char> pending(ops.size(), 0);
   // Open outgoing connections first: connect never waits for the peer's accept,
   // so no ordering between ranks can deadlock here.
+  auto viaShm = [&](const Op &op) { return shm_ && (op.isSend ? shmSend_[op.peer] : shmRecv_[op.peer]) != nullptr; };
   for (auto &op : ops)
-    if (op.isSend && op.peer != bs_->rank()) { void *c; FCXCHECK(sendComm(op.peer, &c)); }
+    if (op.isSend && op.peer != bs_->rank() && !viaShm(op)) { void *c; FCXCHECK(sendComm(op.peer, &c)); }
+  // shared-memory messages: an 8-byte length, then the bytes; state per op
+  struct ShmState {
+    uint64_t header = 0;
+    size_t hdrDone = 0, done = 0;
+  };
+  std::vector<ShmState> shmState(ops.size());
   size_t left = 0;
   for (size_t i = 0; i < ops.size(); ++i) {
     const Op &op = ops[i];
     if (op.peer == bs_->rank()) continue; // self transfers are handled by the callers
+    if (viaShm(op)) {
+      shmState[i].header = op.bytes;
+      pending[i] = 2;
+      ++left;
+      continue;
+    }
     void *c;
     if (op.isSend) {
       FCXCHECK(sendComm(op.peer, &c));
@@ -248,18 +323,62 @@ flagcxResult_t HostNet::run(const std::vector<Op> &ops) {
   }
   uint64_t deadline = nowNs() + (uint64_t)defaultSocketTimeoutMs() * 1000000ull;
   flagcxResult_t firstErr = flagcxSuccess;
+  const int nr = bs_->nranks();
+  std::vector<char> busy(2 * (size_t)nr);
+  uint64_t lastAlive = nowNs();
   while (left) {
     size_t before = left;
+    bool moved = false;
+    std::fill(busy.begin(), busy.end(), 0);
     for (size_t i = 0; i < ops.size(); ++i) {
-      if (!pending[i]) continue;
+      if (pending[i] != 2) continue;
+      const Op &op = ops[i];
+      char &b = busy[(op.isSend ? 0 : nr) + op.peer];
+      if (b) continue; // an earlier message of this ring is still under way
+      ShmState &st = shmState[i];
+      ShmRing &ring = op.isSend ? *shmSend_[op.peer] : *shmRecv_[op.peer];
+      if (st.hdrDone < 8) {
+        uint64_t h = st.header;
+        size_t k = op.isSend ? ring.write((char *)&h + st.hdrDone, 8 - st.hdrDone)
+                             : ring.read((char *)&st.header + st.hdrDone, 8 - st.hdrDone);
+        st.hdrDone += k;
+        moved = moved || k;
+        if (st.hdrDone == 8 && !op.isSend && st.header != op.bytes) {
+          FCX_WARN("host shm: rank %d sent %llu bytes where %zu were expected", op.peer,
+                   (unsigned long long)st.header, op.bytes);
+          return flagcxInternalError;
+        }
+      }
+      if (st.hdrDone == 8 && st.done < op.bytes) {
+        size_t k = op.isSend ? ring.write((char *)op.data + st.done, op.bytes - st.done)
+                             : ring.read((char *)op.data + st.done, op.bytes - st.done);
+        st.done += k;
+        moved = moved || k;
+      }
+      if (st.hdrDone == 8 && st.done == op.bytes) { pending[i] = 0; --left; }
+      else b = 1;
+    }
+    if (moved) deadline = nowNs() + (uint64_t)defaultSocketTimeoutMs() * 1000000ull;
+    else if (nowNs() - lastAlive > 100000000ull) { // nothing moved for a while: is the other side still there?
+      lastAlive = nowNs();
+      for (size_t i = 0; i < ops.size(); ++i)
+        if (pending[i] == 2 && processIsDead(pids_[ops[i].peer])) {
+          FCX_WARN("host shm: rank %d (pid %d) is gone", ops[i].peer, pids_[ops[i].peer]);
+          return flagcxRemoteError;
+        }
+    }
+    for (size_t i = 0; i < ops.size(); ++i) {
+      if (pending[i] != 1) continue;
       int done = 0, sz = 0;
       flagcxResult_t r = net_->test(reqs[i], &done, &sz);
       if (r != flagcxSuccess) { if (firstErr == flagcxSuccess) firstErr = r; done = 1; }
       if (done) { pending[i] = 0; --left; }
     }
     if (left == before) {
-      if (nowNs() > deadline) { FCX_WARN("host net: no progress before the deadline"); return flagcxSystemError; }
-      sched_yield();
+      if (!moved) {
+        if (nowNs() > deadline) { FCX_WARN("host net: no progress before the deadline"); return flagcxSystemError; }
+        sched_yield();
+      }
     } else {
       deadline = nowNs() + (uint64_t)defaultSocketTimeoutMs() * 1000000ull;
     }

@@ -11,8 +11,11 @@
 #pragma once
 #include <vector>
 
+#include <memory>
+
 #include "bootstrap.h"
 #include "flagcx_net.h"
+#include "shm.h"
 
 namespace fcx {
 
@@ -45,6 +48,12 @@ class HostNet {
   void *listen_ = nullptr;
   std::vector<char> handles_; // nranks * FLAGCX_NET_HANDLE_BYTES
   std::vector<void *> send_, recv_;
+  // Ranks of this machine talk through shared-memory rings instead (FLAGCX_HOST_SHM=0
+  // or a net plugin switches that off; all ranks must have got their rings).
+  bool shm_ = false;
+  std::vector<std::unique_ptr<ShmRing>> shmSend_, shmRecv_; // per peer, null: use the adaptor
+  std::vector<int> pids_;
+  flagcxResult_t initShm();
 };
 
 // Element-wise dst = dst (op) src on host memory; used by the collectives and

@@ -14,6 +14,7 @@
 #include "../host/bootstrap.h"
 #include "../host/comm.h"
 #include "../host/cpu_coll.h"
+#include "../host/shm.h"
 #include "../host/tuner.h"
 #include "flagcx_net.h"
 
@@ -208,7 +209,45 @@ static void testHostReduce() {
   EXPECT(getFlagcxDataTypeSize(flagcxBfloat16) == 2 && getFlagcxDataTypeSize((flagcxDataType_t)42) == 0);
 }
 
+// Shared-memory ring: creation rules, wrap-around, a producer and a consumer thread.
+static void testShmRing() {
+  char name[64];
+  snprintf(name, sizeof name, "/flagcx-unit-%d", (int)getpid());
+  ShmRing tx, rx;
+  EXPECT(tx.create(name, 5000) == flagcxInvalidArgument); // not a power of two
+  EXPECT(tx.create(name, 8192) == flagcxSuccess);
+  ShmRing dup;
+  EXPECT(dup.create(name, 8192) == flagcxSystemError); // the name is taken
+  EXPECT(rx.open(name) == flagcxSuccess);
+  ShmRing late;
+  EXPECT(late.open(name) != flagcxSuccess); // the receiver removed the name
+  char small[16] = "hello, ring", got[16] = {0};
+  EXPECT(rx.read(got, sizeof got) == 0);
+  EXPECT(tx.write(small, 12) == 12 && rx.read(got, sizeof got) == 12 && !strcmp(got, small));
+  // far more than the capacity, odd piece sizes so that every wrap position is hit
+  const size_t total = 1 << 20;
+  std::vector<unsigned char> src(total), dst(total, 0);
+  for (size_t i = 0; i < total; ++i) src[i] = (unsigned char)(i * 131 + (i >> 9));
+  std::thread producer([&] {
+    size_t off = 0, piece = 1;
+    while (off < total) {
+      size_t want = std::min(piece, total - off);
+      off += tx.write(src.data() + off, want);
+      piece = piece % 3001 + 7;
+    }
+  });
+  size_t off = 0, piece = 5;
+  while (off < total) {
+    off += rx.read(dst.data() + off, std::min(piece, total - off));
+    piece = piece % 4099 + 11;
+  }
+  producer.join();
+  EXPECT(src == dst);
+  EXPECT(processIsDead(getpid()) == false && processIsDead(0x3ffffff) == true);
+}
+
 int main() {
+  testShmRing();
   testParams();
   testIfMatcher();
   testAddresses();

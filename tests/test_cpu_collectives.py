@@ -18,29 +18,34 @@ def test_version_and_error_strings():
     assert capi.lib().getFlagcxDataTypeSize(capi.DOUBLE) == 8
 
 
-def test_world2_fp32_1mi_elements_matches_numpy():
+@pytest.mark.parametrize("shm", [0, 1])
+def test_world2_fp32_1mi_elements_matches_numpy(shm):
     """The headline CPU configuration: world_size=2, fp32, 1,048,576 elements, seed=rank,
-    1e-6 relative error."""
-    res = run_ranks(2, "host_collectives", 1 << 20, capi.FLOAT)
+    1e-6 relative error.  shm=0: over the socket adaptor; shm=1: over the shared-memory
+    rings that ranks of one machine use by default."""
+    res = run_ranks(2, "host_collectives", 1 << 20, capi.FLOAT, env={"FLAGCX_HOST_SHM": shm})
     for rank, errs in res.items():
         for name, e in errs.items():
             assert e <= 1e-6, (rank, name, e)
 
 
+@pytest.mark.parametrize("shm", [0, 1])
 @pytest.mark.parametrize("n", [1, 3, 4])
-def test_other_world_sizes(n):
-    res = run_ranks(n, "host_collectives", 12 * 1024, capi.DOUBLE)
+def test_other_world_sizes(n, shm):
+    res = run_ranks(n, "host_collectives", 12 * 1024, capi.DOUBLE, env={"FLAGCX_HOST_SHM": shm})
     for errs in res.values():
         assert all(e <= 1e-12 for e in errs.values()), errs
 
 
-def test_every_op_dtype_and_reduction():
-    res = run_ranks(3, "host_all_ops", 1237)
+@pytest.mark.parametrize("shm", [0, 1])
+def test_every_op_dtype_and_reduction(shm):
+    res = run_ranks(3, "host_all_ops", 1237, env={"FLAGCX_HOST_SHM": shm})
     assert all(w <= 1e-5 for w in res.values()), res
 
 
 def test_multi_socket_striping_and_helper_threads():
-    env = {"FLAGCX_NSOCKS_PERTHREAD": 2, "FLAGCX_SOCKET_NTHREADS": 2, "FLAGCX_SOCKET_STRIPE_MIN": 4096}
+    env = {"FLAGCX_NSOCKS_PERTHREAD": 2, "FLAGCX_SOCKET_NTHREADS": 2, "FLAGCX_SOCKET_STRIPE_MIN": 4096,
+           "FLAGCX_HOST_SHM": 0}
     res = run_ranks(2, "host_collectives", 1 << 18, capi.FLOAT, env=env)
     for errs in res.values():
         assert all(e <= 1e-6 for e in errs.values()), errs
@@ -73,8 +78,10 @@ def test_comm_id_environment_rendezvous():
 
 
 # ---- failure detection on the host ---------------------------------------------------
-def test_dead_rank_gives_an_error_not_a_hang():
-    res = run_ranks(3, "rank_that_dies", 1, env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000}, expect_dead=(1,), timeout=60)
+@pytest.mark.parametrize("shm", [0, 1])
+def test_dead_rank_gives_an_error_not_a_hang(shm):
+    res = run_ranks(3, "rank_that_dies", 1, env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000, "FLAGCX_HOST_SHM": shm},
+                    expect_dead=(1,), timeout=60)
     assert set(res) == {0, 2}
     assert all(code in (capi.flagcxRemoteError, capi.flagcxSystemError) for code in res.values()), res
 
@@ -90,8 +97,9 @@ def test_corrupt_unique_id_is_rejected():
     assert res[0] == capi.flagcxInvalidArgument
 
 
-def test_mismatched_message_sizes_are_detected():
-    res = run_ranks(2, "mismatched_sizes", env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000}, timeout=60)
+@pytest.mark.parametrize("shm", [0, 1])
+def test_mismatched_message_sizes_are_detected(shm):
+    res = run_ranks(2, "mismatched_sizes", env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000, "FLAGCX_HOST_SHM": shm}, timeout=60)
     assert res[1] in (capi.flagcxInternalError, capi.flagcxRemoteError, capi.flagcxSystemError), res
 
 
@@ -193,6 +201,7 @@ def test_c_api_example_program_forks_its_ranks_and_checks_results():
 @pytest.mark.parametrize("n,seed", [(2, 1), (4, 2), (5, 3)])
 def test_random_schedule_with_per_rank_delays(n, seed):
     """Back-to-back collectives of random kind and size while the ranks drift apart by
-    random sleeps: connections, tags and buffers must never get mixed up."""
-    res = run_ranks(n, "host_random_stress", 40, seed, timeout=180)
+    random sleeps: connections, tags and buffers must never get mixed up.  Odd seeds run
+    over sockets, even ones over shared memory."""
+    res = run_ranks(n, "host_random_stress", 40, seed, env={"FLAGCX_HOST_SHM": int(seed % 2 == 0)}, timeout=180)
     assert all(v < 1e-5 for v in res.values()), res
