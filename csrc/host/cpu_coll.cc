@@ -186,7 +186,7 @@ flagcxResult_t HostNet::initShm() {
   infos[me] = {hostHash(), (int32_t)getpid(), 0};
   const bool want = n > 1 && readParam("HOST_SHM", 1) != 0 && !strcmp(net_->name, "socket");
   FCXCHECK(bs_->allGather(infos.data(), sizeof(Info)));
-  size_t cap = (size_t)std::max<int64_t>(4096, readParam("SHM_RING_BYTES", 1 << 20));
+  size_t cap = (size_t)std::max<int64_t>(4096, readParam("SHM_RING_BYTES", 512 << 10));
   while (cap & (cap - 1)) cap &= cap - 1; // round down to a power of two
   auto nameOf = [&](int src, int dst) {
     char b[96];
