@@ -646,3 +646,31 @@ def host_random_stress(rank, n, uid, rounds, seed):
     comm.barrier()
     comm.destroy()
     return worst
+
+
+def gpu_buffers_over_sockets(rank, n, uid):
+    """Device buffers on ranks that may not use NVLink (FLAGCX_FORCE_HOST=1): staged through
+    pinned memory over the host path.  No kernel of one rank waits for another, so the
+    ranks may share a GPU."""
+    import torch
+    torch.cuda.set_device(0)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    assert not comm.device_path
+    count = 100003
+    xs = [_torch_seeded(r, count, torch.float32) for r in range(n)]
+    x = xs[rank].cuda()
+    out = torch.empty_like(x)
+    comm.all_reduce(x, out, count, capi.FLOAT, capi.SUM)
+    torch.cuda.synchronize()
+    ref = torch.stack(xs).double().sum(0)
+    worst = {"allreduce": float(((out.cpu().double() - ref).abs() / ref.abs().clamp(min=1)).max())}
+    comm.all_reduce(x, x, count, capi.FLOAT, capi.SUM)  # in place
+    torch.cuda.synchronize()
+    worst["allreduce_inplace"] = float(((x.cpu().double() - ref).abs() / ref.abs().clamp(min=1)).max())
+    ag = torch.empty(count * n, device="cuda")
+    comm.all_gather(xs[rank].cuda(), ag, count, capi.FLOAT)
+    torch.cuda.synchronize()
+    worst["allgather"] = float(not torch.equal(ag.cpu(), torch.cat(xs)))
+    comm.barrier()
+    comm.destroy()
+    return worst

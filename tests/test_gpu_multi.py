@@ -37,3 +37,11 @@ def test_missing_peer_becomes_an_error_code():
     env = {"NCCL_NVLS_ENABLE": "0", "FLAGCX_NVLS_ENABLE": "0"}
     res = run_ranks(n, "gpu_peer_never_launches", env=env, timeout=120)
     assert res[0] == capi.flagcxRemoteError
+
+
+@pytest.mark.skipif(ngpus() < 1, reason="needs a GPU")
+def test_device_buffers_without_peer_access_go_over_the_host_path():
+    """What two machines, or FLAGCX_HOSTID-split ranks of one machine, fall back to."""
+    res = run_ranks(2, "gpu_buffers_over_sockets", env={"FLAGCX_FORCE_HOST": "1"}, timeout=120)
+    for rank, worst in res.items():
+        assert all(v < 1e-5 for v in worst.values()), (rank, worst)
