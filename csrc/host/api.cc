@@ -138,6 +138,19 @@ flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks, flagcxUniqueId
   *comm = nullptr;
   FCXCHECK(commCreate(comm, nranks, *commId, rank));
   if (int64_t cap = readParam("TRACE", 0)) (*comm)->trace.enable((int)std::min<int64_t>(cap, 1 << 20));
+  // FLAGCX_USE_TUNER=1 (name kept from the FlagCX project): measure at init unless a
+  // table was loaded from FLAGCX_TUNE_FILE; rank 0 then writes the table there.
+  flagcxComm *c = *comm;
+  if (readParam("USE_TUNER", 0) != 0 && c->devicePath && !c->emu && c->tuner && nranks > 1 && c->tuner->table.empty()) {
+    const size_t lo = (size_t)std::max<int64_t>(1024, readParam("TUNER_MIN_BYTES", 64 << 10));
+    const size_t hi = (size_t)std::max<int64_t>((int64_t)lo, readParam("TUNER_MAX_BYTES", 64 << 20));
+    for (flagcxCommOp_t op : {flagcxCommOpAllReduce, flagcxCommOpAllGather, flagcxCommOpReduceScatter, flagcxCommOpAlltoAll}) {
+      flagcxResult_t r = c->tuner->tune(c, op, flagcxBfloat16, lo, hi, 5);
+      if (r != flagcxSuccess) { FCX_WARN("FLAGCX_USE_TUNER: tuning %s failed (%d); heuristics stay in force", commOpName(op), (int)r); break; }
+    }
+    if (const char *f = getEnv("FLAGCX_TUNE_FILE"))
+      if (rank == 0 && !c->tuner->table.empty()) c->tuner->save(f);
+  }
   return flagcxSuccess;
 }
 
