@@ -575,12 +575,39 @@ flagcxResult_t flagcxOneSideRegister(flagcxComm_t comm, void *buff, size_t size)
   FCX_COMMCHECK(comm);
   if (!comm->devicePath) return flagcxNotSupported;
   Window *w = comm->windows.find(buff, size);
+  const bool created = w == nullptr;
   if (!w) {
     if (comm->emu) FCXCHECK(emuWindowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
     else FCXCHECK(windowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
   }
   comm->oneSideData.push_back(w);
+  comm->oneSideOwned.push_back(created ? 1 : 0);
   return flagcxSuccess;
+}
+
+// Collective: forgets every memory region of flagcxOneSideRegister (indices start at 0
+// again) and unmaps the windows that call created.  Declared in
+// flagcx_kernel_internal.h in the FlagCX project.
+flagcxResult_t flagcxOneSideDeregister(flagcxComm_t comm) {
+  FCX_COMMCHECK(comm);
+  if (!comm->devicePath) return flagcxNotSupported;
+  flagcxResult_t first = flagcxSuccess;
+  for (size_t i = 0; i < comm->oneSideData.size(); ++i) {
+    if (!comm->oneSideOwned[i]) continue;
+    flagcxResult_t r = flagcxCommWindowDeregister(comm, (flagcxWindow_t)comm->oneSideData[i], flagcxMemCCL);
+    if (r != flagcxSuccess && first == flagcxSuccess) first = r;
+  }
+  comm->oneSideData.clear();
+  comm->oneSideOwned.clear();
+  return first;
+}
+flagcxResult_t flagcxOneSideSignalDeregister(flagcxComm_t comm) {
+  FCX_COMMCHECK(comm);
+  if (!comm->devicePath) return flagcxNotSupported;
+  flagcxResult_t r = flagcxSuccess;
+  if (comm->oneSideSignalWin) r = flagcxCommWindowDeregister(comm, (flagcxWindow_t)comm->oneSideSignalWin, flagcxMemCCL);
+  comm->oneSideSignalWin = nullptr;
+  return r;
 }
 flagcxResult_t flagcxOneSideSignalRegister(const flagcxComm_t comm, void *buff, size_t size, int) {
   FCX_COMMCHECK(comm);

@@ -125,6 +125,7 @@ struct flagcxComm {
   std::vector<uint64_t> signalSeen; // per-peer count consumed by flagcxWaitSignal
   fcx::WindowRegistry windows;
   std::vector<fcx::Window *> oneSideData; // memory regions in registration order
+  std::vector<char> oneSideOwned;         // 1: the window was created by flagcxOneSideRegister
   cudaStream_t internalStream = nullptr;
   std::unique_ptr<fcx::Tuner> tuner;
 

@@ -88,6 +88,13 @@ flagcxResult_t flagcxCommSetWaitTimeoutMs(flagcxComm_t comm, int ms);
 flagcxResult_t flagcxWindowGetPeerPointer(flagcxWindow_t win, int peer, size_t offset, void **ptr);
 flagcxResult_t flagcxWindowGetMulticastPointer(flagcxWindow_t win, size_t offset, void **ptr);
 
+/* ---- one-sided API: release --------------------------------------------------------------
+ * Collective.  flagcxOneSideDeregister forgets all memory regions of flagcxOneSideRegister
+ * (region indices start at 0 again) and unmaps the windows those calls created;
+ * flagcxOneSideSignalDeregister releases the signal buffer's window. */
+flagcxResult_t flagcxOneSideDeregister(flagcxComm_t comm);
+flagcxResult_t flagcxOneSideSignalDeregister(flagcxComm_t comm);
+
 /* ---- emulated world ----------------------------------------------------------------
  * nranks communicators inside one process on one GPU.  A collective call on one
  * of them is parked until all of them have made the matching call; the last call

@@ -205,3 +205,14 @@ def test_random_schedule_with_per_rank_delays(n, seed):
     over sockets, even ones over shared memory."""
     res = run_ranks(n, "host_random_stress", 40, seed, env={"FLAGCX_HOST_SHM": int(seed % 2 == 0)}, timeout=180)
     assert all(v < 1e-5 for v in res.values()), res
+
+
+def test_one_sided_calls_say_not_supported_without_an_nvlink_domain():
+    comm = capi.Comm.init_rank(1, capi.get_unique_id(), 0)
+    buf = np.zeros(1024, np.uint8)
+    lib = capi.lib()
+    p = capi.C.c_void_p(buf.ctypes.data)
+    assert lib.flagcxOneSideRegister(comm.h, p, capi.C.c_size_t(buf.nbytes)) == capi.flagcxNotSupported
+    assert lib.flagcxOneSideDeregister(comm.h) == capi.flagcxNotSupported
+    assert lib.flagcxOneSideSignalDeregister(comm.h) == capi.flagcxNotSupported
+    comm.destroy()
