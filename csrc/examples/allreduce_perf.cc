@@ -1,12 +1,15 @@
 // allreduce_perf.cc -- a program written against the public C API only: launches N ranks
 // (one process each, one GPU each when GPUs are present, host buffers otherwise), runs
-// all-reduce over a range of sizes, checks the result and prints time, algorithm
-// bandwidth and bus bandwidth.  Same role as test/perf/host_api/test_allreduce.cpp in the
-// FlagCX project, without mpirun: ranks are forked here and meet through FLAGCX_COMM_ID.
+// one collective (-o allreduce|allgather|reducescatter|alltoall|broadcast, default
+// allreduce) over a range of sizes, checks the result and prints time, algorithm
+// bandwidth and bus bandwidth.  Same role as the test/perf/host_api/test_*.cpp programs of
+// the FlagCX project, without mpirun: ranks are forked here and meet through
+// FLAGCX_COMM_ID.
 //
 //   make -C csrc examples
 //   csrc/build/examples/allreduce_perf -n 8 -b 1M -e 1G -f 2 -w 5 -i 20
-//   csrc/build/examples/allreduce_perf -n 3 --host -b 1K -e 1M        (CPU ranks over sockets)
+//   csrc/build/examples/allreduce_perf -n 3 --host -b 1K -e 1M        (CPU ranks, host buffers)
+//   csrc/build/examples/allreduce_perf -n 8 -o alltoall -b 1M -e 256M
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -43,7 +46,36 @@ static size_t parseSize(const char *s) {
   return (size_t)v;
 }
 
-static int runRank(int rank, int n, bool host, size_t minBytes, size_t maxBytes, int factor, int warmup, int iters) {
+enum Op { kAllReduce, kAllGather, kReduceScatter, kAllToAll, kBroadcast };
+
+// `bytes` is the size of the larger of the two buffers; count = elements of the call.
+static flagcxResult_t runOp(Op op, const void *send, void *recv, size_t total, int n, flagcxComm_t comm,
+                            flagcxStream_t stream) {
+  switch (op) {
+    case kAllReduce: return flagcxAllReduce(send, recv, total, flagcxFloat, flagcxSum, comm, stream);
+    case kAllGather: return flagcxAllGather(send, recv, total / n, flagcxFloat, comm, stream);
+    case kReduceScatter: return flagcxReduceScatter(send, recv, total / n, flagcxFloat, flagcxSum, comm, stream);
+    case kAllToAll: return flagcxAlltoAll(send, recv, total / n, flagcxFloat, comm, stream);
+    case kBroadcast: return flagcxBroadcast(send, recv, total, flagcxFloat, 0, comm, stream);
+  }
+  return flagcxInvalidArgument;
+}
+
+// What element i of the output must hold when rank r's input element j is (j % 13) + r.
+static float expected(Op op, size_t i, size_t total, int n, int rank) {
+  const size_t per = total / n;
+  const float ranks = (float)(n * (n - 1) / 2);
+  switch (op) {
+    case kAllReduce: return (float)n * (float)(i % 13) + ranks;
+    case kAllGather: return (float)((i % per) % 13) + (float)(i / per);
+    case kReduceScatter: return (float)n * (float)((rank * per + i) % 13) + ranks;
+    case kAllToAll: return (float)((rank * per + i % per) % 13) + (float)(i / per);
+    case kBroadcast: return (float)(i % 13);
+  }
+  return 0.f;
+}
+
+static int runRank(Op op, int rank, int n, bool host, size_t minBytes, size_t maxBytes, int factor, int warmup, int iters) {
   gRank = rank;
   flagcxDeviceHandle_t dev;
   CHECK(flagcxDeviceHandleInit(&dev));
@@ -72,17 +104,20 @@ static int runRank(int rank, int n, bool host, size_t minBytes, size_t maxBytes,
   CHECK(dev->deviceMemcpy(send, h.data(), maxBytes, flagcxMemcpyHostToDevice, stream));
   CHECK(dev->streamSynchronize(stream));
 
-  if (rank == 0) printf("# %d ranks, %s buffers\n# %12s %10s %10s %10s %8s\n", n, onGpu ? "device" : "host", "bytes",
-                        "time(us)", "algbw GB/s", "busbw GB/s", "check");
+  static const char *names[] = {"allreduce", "allgather", "reducescatter", "alltoall", "broadcast"};
+  if (rank == 0) printf("# %s, %d ranks, %s buffers\n# %12s %10s %10s %10s %8s\n", names[op], n, onGpu ? "device" : "host",
+                        "bytes", "time(us)", "algbw GB/s", "busbw GB/s", "check");
   int bad = 0;
   for (size_t bytes = minBytes; bytes <= maxBytes; bytes *= factor) {
-    const size_t count = bytes / 4;
-    for (int i = 0; i < warmup; ++i) CHECK(flagcxAllReduce(send, recv, count, flagcxFloat, flagcxSum, comm, stream));
+    const size_t count = bytes / 4 / n * n; // elements of the larger buffer, a multiple of the ranks
+    if (count == 0) continue;
+    const size_t outCount = op == kReduceScatter ? count / n : count;
+    for (int i = 0; i < warmup; ++i) CHECK(runOp(op, send, recv, count, n, comm, stream));
     CHECK(dev->streamSynchronize(stream));
     CHECK(flagcxBarrier(comm, stream));
     CHECK(dev->streamSynchronize(stream));
     CHECK(dev->eventRecord(e0, stream));
-    for (int i = 0; i < iters; ++i) CHECK(flagcxAllReduce(send, recv, count, flagcxFloat, flagcxSum, comm, stream));
+    for (int i = 0; i < iters; ++i) CHECK(runOp(op, send, recv, count, n, comm, stream));
     CHECK(dev->eventRecord(e1, stream));
     CHECK(dev->eventSynchronize(e1));
     float ms = 0;
@@ -103,17 +138,18 @@ static int runRank(int rank, int n, bool host, size_t minBytes, size_t maxBytes,
       dev->deviceFree(a, where, stream);
       dev->deviceFree(o, where, stream);
     }
-    CHECK(dev->deviceMemcpy(back.data(), recv, bytes, flagcxMemcpyDeviceToHost, stream));
+    CHECK(dev->deviceMemcpy(back.data(), recv, outCount * 4, flagcxMemcpyDeviceToHost, stream));
     CHECK(dev->streamSynchronize(stream));
     bool ok = true;
-    for (size_t i = 0; i < count && ok; i += (count / 257) + 1) {
-      float want = (float)n * (float)(i % 13) + (float)(n * (n - 1) / 2);
+    for (size_t i = 0; i < outCount && ok; i += (outCount / 257) + 1) {
+      float want = expected(op, i, count, n, rank);
       ok = std::fabs(back[i] - want) <= 1e-5f * std::fabs(want) + 1e-6f;
     }
     bad += !ok;
     if (rank == 0) {
-      double alg = (double)bytes / worst / 1e3;
-      printf("  %12zu %10.1f %10.2f %10.2f %8s\n", bytes, worst, alg, alg * 2.0 * (n - 1) / n, ok ? "ok" : "WRONG");
+      double alg = (double)(count * 4) / worst / 1e3;
+      double factorBus = op == kAllReduce ? 2.0 * (n - 1) / n : op == kBroadcast ? 1.0 : (double)(n - 1) / n;
+      printf("  %12zu %10.1f %10.2f %10.2f %8s\n", count * 4, worst, alg, alg * factorBus, ok ? "ok" : "WRONG");
       fflush(stdout);
     }
     if (bytes == 0 || factor < 2) break;
@@ -132,6 +168,7 @@ int main(int argc, char **argv) {
   int n = 2, factor = 2, warmup = 5, iters = 20, port = 0;
   size_t minBytes = 1 << 20, maxBytes = 64 << 20;
   bool host = false;
+  Op op = kAllReduce;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     auto next = [&]() -> const char * { return i + 1 < argc ? argv[++i] : "0"; };
@@ -143,7 +180,16 @@ int main(int argc, char **argv) {
     else if (a == "-i") iters = atoi(next());
     else if (a == "-p") port = atoi(next());
     else if (a == "--host") host = true;
-    else { fprintf(stderr, "usage: %s [-n ranks] [-b min] [-e max] [-f factor] [-w warmup] [-i iters] [-p port] [--host]\n", argv[0]); return 64; }
+    else if (a == "-o") {
+      std::string o = next();
+      if (o == "allreduce") op = kAllReduce;
+      else if (o == "allgather") op = kAllGather;
+      else if (o == "reducescatter") op = kReduceScatter;
+      else if (o == "alltoall") op = kAllToAll;
+      else if (o == "broadcast") op = kBroadcast;
+      else { fprintf(stderr, "unknown operation %s\n", o.c_str()); return 64; }
+    }
+    else { fprintf(stderr, "usage: %s [-n ranks] [-b min] [-e max] [-f factor] [-w warmup] [-i iters] [-p port] [-o op] [--host]\n", argv[0]); return 64; }
   }
   minBytes = (minBytes + 3) / 4 * 4;
   if (maxBytes < minBytes) maxBytes = minBytes;
@@ -156,7 +202,7 @@ int main(int argc, char **argv) {
   std::vector<pid_t> kids;
   for (int r = 0; r < n; ++r) {
     pid_t p = fork();
-    if (p == 0) return runRank(r, n, host, minBytes, maxBytes, factor, warmup, iters);
+    if (p == 0) return runRank(op, r, n, host, minBytes, maxBytes, factor, warmup, iters);
     if (p < 0) { perror("fork"); return 1; }
     kids.push_back(p);
   }

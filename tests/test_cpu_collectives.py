@@ -192,10 +192,11 @@ def test_c_api_example_program_forks_its_ranks_and_checks_results():
         port = s.getsockname()[1]
     exe = os.path.join(root, "csrc", "build", "examples", "allreduce_perf")
     env = {k: v for k, v in os.environ.items() if k != "FLAGCX_COMM_ID"}
-    res = subprocess.run([exe, "-n", "3", "--host", "-b", "1K", "-e", "256K", "-f", "4", "-w", "1", "-i", "2", "-p", str(port)],
-                         capture_output=True, text=True, timeout=120, env=env)
-    assert res.returncode == 0, res.stdout + res.stderr
-    assert res.stdout.count(" ok") == 5 and "WRONG" not in res.stdout, res.stdout
+    for op in ("allreduce", "allgather", "reducescatter", "alltoall", "broadcast"):
+        res = subprocess.run([exe, "-n", "3", "--host", "-o", op, "-b", "1K", "-e", "256K", "-f", "4", "-w", "1", "-i", "2",
+                              "-p", str(port)], capture_output=True, text=True, timeout=120, env=env)
+        assert res.returncode == 0, op + res.stdout + res.stderr
+        assert res.stdout.count(" ok") == 5 and "WRONG" not in res.stdout, op + res.stdout
 
 
 @pytest.mark.parametrize("n,seed", [(2, 1), (4, 2), (5, 3)])
