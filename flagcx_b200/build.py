@@ -19,8 +19,25 @@ def build_core(jobs: int | None = None, verbose: bool = False) -> str:
     return os.path.join(ROOT, "flagcx_b200", "lib", "libflagcx.so")
 
 
+def build_devtest(verbose: bool = False) -> str:
+    """The device-API conformance kernels (csrc/tests/device_api_kernels.cu) as a shared
+    library next to their source; tests/test_gpu_device_api.py loads it."""
+    src = os.path.join(ROOT, "csrc", "tests", "device_api_kernels.cu")
+    lib = os.path.join(ROOT, "csrc", "tests", "libflagcx_devtest.so")
+    if os.path.exists(lib) and os.path.getmtime(lib) >= os.path.getmtime(src):
+        return lib
+    cmd = ["/usr/local/cuda/bin/nvcc", "-std=c++17", "-O2", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+           "-shared", "-Xcompiler", "-fPIC", "-cudart", "shared", "-I" + os.path.join(ROOT, "csrc", "include"), src, "-o", lib]
+    res = subprocess.run(cmd, capture_output=not verbose, text=True)
+    if res.returncode != 0:
+        sys.stderr.write((res.stdout or "") + (res.stderr or ""))
+        raise RuntimeError("building the device-API test kernels failed")
+    return lib
+
+
 def build(verbose: bool = False) -> None:
     build_core(verbose=verbose)
+    build_devtest(verbose=verbose)
     try:
         from flagcx_b200.torch_backend import build as tb
     except ImportError:
