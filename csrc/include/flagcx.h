@@ -150,15 +150,12 @@ typedef struct {
  */
 struct flagcxDeviceHandle {
   flagcxResult_t (*deviceSynchronize)();
-  flagcxResult_t (*deviceMemcpy)(void *dst, void *src, size_t size,
-                                 flagcxMemcpyType_t type,
-                                 flagcxStream_t stream);
-  flagcxResult_t (*deviceMemset)(void *ptr, int value, size_t size,
-                                 flagcxMemType_t type, flagcxStream_t stream);
-  flagcxResult_t (*deviceMalloc)(void **ptr, size_t size, flagcxMemType_t type,
-                                 flagcxStream_t stream);
-  flagcxResult_t (*deviceFree)(void *ptr, flagcxMemType_t type,
-                               flagcxStream_t stream);
+  flagcxResult_t (*deviceMemcpy)(void *dst, void *src, size_t size, flagcxMemcpyType_t type,
+      flagcxStream_t stream);
+  flagcxResult_t (*deviceMemset)(void *ptr, int value, size_t size, flagcxMemType_t type,
+      flagcxStream_t stream);
+  flagcxResult_t (*deviceMalloc)(void **ptr, size_t size, flagcxMemType_t type, flagcxStream_t stream);
+  flagcxResult_t (*deviceFree)(void *ptr, flagcxMemType_t type, flagcxStream_t stream);
   flagcxResult_t (*setDevice)(int dev);
   flagcxResult_t (*getDevice)(int *dev);
   flagcxResult_t (*getDeviceCount)(int *count);
@@ -171,19 +168,15 @@ struct flagcxDeviceHandle {
   flagcxResult_t (*streamSynchronize)(flagcxStream_t stream);
   flagcxResult_t (*streamQuery)(flagcxStream_t stream);
   flagcxResult_t (*streamWaitEvent)(flagcxStream_t stream, flagcxEvent_t event);
-  flagcxResult_t (*eventCreate)(flagcxEvent_t *event,
-                                flagcxEventType_t eventType);
+  flagcxResult_t (*eventCreate)(flagcxEvent_t *event, flagcxEventType_t eventType);
   flagcxResult_t (*eventDestroy)(flagcxEvent_t event);
   flagcxResult_t (*eventRecord)(flagcxEvent_t event, flagcxStream_t stream);
   flagcxResult_t (*eventSynchronize)(flagcxEvent_t event);
   flagcxResult_t (*eventQuery)(flagcxEvent_t event);
-  flagcxResult_t (*eventElapsedTime)(float *ms, flagcxEvent_t start,
-                                     flagcxEvent_t end);
-  flagcxResult_t (*ipcMemHandleCreate)(flagcxIpcMemHandle_t *handle,
-                                       size_t *size);
+  flagcxResult_t (*eventElapsedTime)(float *ms, flagcxEvent_t start, flagcxEvent_t end);
+  flagcxResult_t (*ipcMemHandleCreate)(flagcxIpcMemHandle_t *handle, size_t *size);
   flagcxResult_t (*ipcMemHandleGet)(flagcxIpcMemHandle_t handle, void *devPtr);
-  flagcxResult_t (*ipcMemHandleOpen)(flagcxIpcMemHandle_t handle,
-                                     void **devPtr);
+  flagcxResult_t (*ipcMemHandleOpen)(flagcxIpcMemHandle_t handle, void **devPtr);
   flagcxResult_t (*ipcMemHandleClose)(void *devPtr);
   flagcxResult_t (*ipcMemHandleFree)(flagcxIpcMemHandle_t handle);
 };
@@ -219,40 +212,29 @@ typedef enum {
 
 /* Allocate / free peer-shareable device memory (2 MiB granularity). On a host
  * without a GPU this returns page-aligned host memory. */
-flagcxResult_t flagcxMemAlloc(void **ptr, size_t size,
-                              flagcxMemAllocator_t allocator
-                                  FLAGCX_DEFAULT_ALLOCATOR);
-flagcxResult_t flagcxMemFree(void *ptr, flagcxMemAllocator_t allocator
-                                            FLAGCX_DEFAULT_ALLOCATOR);
+flagcxResult_t flagcxMemAlloc(void **ptr, size_t size, flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
+flagcxResult_t flagcxMemFree(void *ptr, flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
 
 /* Local registration: remembers [buff, buff+size) so that later collectives on
  * it can skip the staging copy once a window covers it. */
-flagcxResult_t flagcxCommRegister(const flagcxComm_t comm, void *buff,
-                                  size_t size, void **handle,
-                                  flagcxMemAllocator_t allocator
-                                      FLAGCX_DEFAULT_ALLOCATOR);
+flagcxResult_t flagcxCommRegister(const flagcxComm_t comm, void *buff, size_t size, void **handle,
+    flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
 flagcxResult_t flagcxCommDeregister(const flagcxComm_t comm, void *handle,
-                                    flagcxMemAllocator_t allocator
-                                        FLAGCX_DEFAULT_ALLOCATOR);
+    flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
 
 /* Collective: every rank passes a buffer of the same size obtained from
  * flagcxMemAlloc; afterwards every local peer has it mapped and collectives
  * whose arguments fall inside the window run without staging. */
-flagcxResult_t flagcxCommWindowRegister(flagcxComm_t comm, void *buff,
-                                        size_t size, flagcxWindow_t *win,
-                                        int winFlags,
-                                        flagcxMemAllocator_t allocator
-                                            FLAGCX_DEFAULT_ALLOCATOR);
+flagcxResult_t flagcxCommWindowRegister(flagcxComm_t comm, void *buff, size_t size, flagcxWindow_t *win,
+    int winFlags, flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
 flagcxResult_t flagcxCommWindowDeregister(flagcxComm_t comm, flagcxWindow_t win,
-                                          flagcxMemAllocator_t allocator
-                                              FLAGCX_DEFAULT_ALLOCATOR);
+    flagcxMemAllocator_t allocator FLAGCX_DEFAULT_ALLOCATOR);
 
 /* ---- communicator life cycle -------------------------------------------- */
 flagcxResult_t flagcxIsHomoComm(flagcxComm_t comm, int *isHomo);
 flagcxResult_t flagcxGetVersion(int *version);
 flagcxResult_t flagcxGetUniqueId(flagcxUniqueId_t uniqueId);
-flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks,
-                                  flagcxUniqueId_t commId, int rank);
+flagcxResult_t flagcxCommInitRank(flagcxComm_t *comm, int nranks, flagcxUniqueId_t commId, int rank);
 flagcxResult_t flagcxCommFinalize(flagcxComm_t comm);
 flagcxResult_t flagcxCommDestroy(flagcxComm_t comm);
 /* Abort raises a flag that every device-side wait of this communicator polls,
@@ -264,88 +246,59 @@ const char *flagcxGetErrorString(flagcxResult_t result);
 const char *flagcxGetLastError(flagcxComm_t comm);
 /* Reports a device-side wait that ran out of time, an abort, or a socket
  * failure seen by the watchdog thread since the communicator was created. */
-flagcxResult_t flagcxCommGetAsyncError(flagcxComm_t comm,
-                                       flagcxResult_t *asyncError);
+flagcxResult_t flagcxCommGetAsyncError(flagcxComm_t comm, flagcxResult_t *asyncError);
 flagcxResult_t flagcxCommCount(const flagcxComm_t comm, int *count);
 flagcxResult_t flagcxCommGetDeviceNumber(const flagcxComm_t comm, int *device);
 flagcxResult_t flagcxCommUserRank(const flagcxComm_t comm, int *rank);
 
 /* ---- collectives --------------------------------------------------------- */
 flagcxResult_t flagcxBarrier(flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxReduce(const void *sendbuff, void *recvbuff, size_t count,
-                            flagcxDataType_t datatype, flagcxRedOp_t op,
-                            int root, flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxGather(const void *sendbuff, void *recvbuff, size_t count,
-                            flagcxDataType_t datatype, int root,
-                            flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxScatter(const void *sendbuff, void *recvbuff, size_t count,
-                             flagcxDataType_t datatype, int root,
-                             flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxBroadcast(const void *sendbuff, void *recvbuff,
-                               size_t count, flagcxDataType_t datatype,
-                               int root, flagcxComm_t comm,
-                               flagcxStream_t stream);
-flagcxResult_t flagcxAllReduce(const void *sendbuff, void *recvbuff,
-                               size_t count, flagcxDataType_t datatype,
-                               flagcxRedOp_t op, flagcxComm_t comm,
-                               flagcxStream_t stream);
-flagcxResult_t flagcxReduceScatter(const void *sendbuff, void *recvbuff,
-                                   size_t recvcount, flagcxDataType_t datatype,
-                                   flagcxRedOp_t op, flagcxComm_t comm,
-                                   flagcxStream_t stream);
-flagcxResult_t flagcxAllGather(const void *sendbuff, void *recvbuff,
-                               size_t sendcount, flagcxDataType_t datatype,
-                               flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxAlltoAll(const void *sendbuff, void *recvbuff,
-                              size_t count, flagcxDataType_t datatype,
-                              flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxAlltoAllv(const void *sendbuff, size_t *sendcounts,
-                               size_t *sdispls, void *recvbuff,
-                               size_t *recvcounts, size_t *rdispls,
-                               flagcxDataType_t datatype, flagcxComm_t comm,
-                               flagcxStream_t stream);
-flagcxResult_t flagcxSend(const void *sendbuff, size_t count,
-                          flagcxDataType_t datatype, int peer,
-                          flagcxComm_t comm, flagcxStream_t stream);
-flagcxResult_t flagcxRecv(void *recvbuff, size_t count,
-                          flagcxDataType_t datatype, int peer,
-                          flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    flagcxRedOp_t op, int root, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxGather(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    int root, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxScatter(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    int root, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxBroadcast(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    int root, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAllReduce(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    flagcxRedOp_t op, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxReduceScatter(const void *sendbuff, void *recvbuff, size_t recvcount,
+    flagcxDataType_t datatype, flagcxRedOp_t op, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAllGather(const void *sendbuff, void *recvbuff, size_t sendcount,
+    flagcxDataType_t datatype, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAlltoAll(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
+    flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxAlltoAllv(const void *sendbuff, size_t *sendcounts, size_t *sdispls, void *recvbuff,
+    size_t *recvcounts, size_t *rdispls, flagcxDataType_t datatype, flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxSend(const void *sendbuff, size_t count, flagcxDataType_t datatype, int peer,
+    flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxRecv(void *recvbuff, size_t count, flagcxDataType_t datatype, int peer, flagcxComm_t comm,
+    flagcxStream_t stream);
 
 /* ---- one-sided host API --------------------------------------------------- */
 /* Collective registration of a data buffer (index returned in call order: the
  * first registered buffer is memory region 0, the next 1, ...). */
-flagcxResult_t flagcxOneSideRegister(flagcxComm_t comm, void *buff,
-                                     size_t size);
-flagcxResult_t flagcxOneSideSignalRegister(const flagcxComm_t comm, void *buff,
-                                           size_t size, int ptrType);
-flagcxResult_t flagcxOneSideStagingRegister(const flagcxComm_t comm, void *buff,
-                                            size_t size);
+flagcxResult_t flagcxOneSideRegister(flagcxComm_t comm, void *buff, size_t size);
+flagcxResult_t flagcxOneSideSignalRegister(const flagcxComm_t comm, void *buff, size_t size, int ptrType);
+flagcxResult_t flagcxOneSideStagingRegister(const flagcxComm_t comm, void *buff, size_t size);
 flagcxResult_t flagcxOneSideStagingDeregister(const flagcxComm_t comm);
-flagcxResult_t flagcxGet(flagcxComm_t comm, int peer, size_t srcOffset,
-                         size_t dstOffset, size_t size, int srcMrIdx,
-                         int dstMrIdx);
-flagcxResult_t flagcxPut(flagcxComm_t comm, int peer, size_t srcOffset,
-                         size_t dstOffset, size_t size, int srcMrIdx,
-                         int dstMrIdx);
-flagcxResult_t flagcxBatchPut(flagcxComm_t comm, int peer,
-                              const size_t *srcOffsets,
-                              const size_t *dstOffsets, const size_t *sizes,
-                              const int *srcMrIdxs, const int *dstMrIdxs,
-                              size_t count);
-flagcxResult_t flagcxPutSignal(const void *localbuff, size_t count,
-                               flagcxDataType_t datatype, int peer,
-                               flagcxWindow_t peerWin, size_t peerWinOffset,
-                               unsigned int flags, flagcxComm_t comm,
-                               flagcxStream_t stream);
-flagcxResult_t flagcxSignal(int peer, unsigned int flags, flagcxComm_t comm,
-                            flagcxStream_t stream);
+flagcxResult_t flagcxGet(flagcxComm_t comm, int peer, size_t srcOffset, size_t dstOffset, size_t size,
+    int srcMrIdx, int dstMrIdx);
+flagcxResult_t flagcxPut(flagcxComm_t comm, int peer, size_t srcOffset, size_t dstOffset, size_t size,
+    int srcMrIdx, int dstMrIdx);
+flagcxResult_t flagcxBatchPut(flagcxComm_t comm, int peer, const size_t *srcOffsets, const size_t *dstOffsets,
+    const size_t *sizes, const int *srcMrIdxs, const int *dstMrIdxs, size_t count);
+flagcxResult_t flagcxPutSignal(const void *localbuff, size_t count, flagcxDataType_t datatype, int peer,
+    flagcxWindow_t peerWin, size_t peerWinOffset, unsigned int flags, flagcxComm_t comm,
+    flagcxStream_t stream);
+flagcxResult_t flagcxSignal(int peer, unsigned int flags, flagcxComm_t comm, flagcxStream_t stream);
 typedef struct {
   uint64_t opCnt; /* how many signals to wait for from `peer` */
   int peer;
 } flagcxWaitSignalDesc_t;
-flagcxResult_t flagcxWaitSignal(int nDesc,
-                                const flagcxWaitSignalDesc_t *signalDescs,
-                                flagcxComm_t comm, flagcxStream_t stream);
+flagcxResult_t flagcxWaitSignal(int nDesc, const flagcxWaitSignalDesc_t *signalDescs, flagcxComm_t comm,
+    flagcxStream_t stream);
 flagcxResult_t flagcxReadCounter(flagcxComm_t comm, uint64_t *count);
 flagcxResult_t flagcxWaitCounter(flagcxComm_t comm, uint64_t target);
 
