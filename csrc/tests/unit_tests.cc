@@ -166,6 +166,43 @@ static void testBootstrapThreads() {
   EXPECT(bad.load() == 0);
 }
 
+// Whole communicators as threads of one process (host buffers): the public API from
+// several threads at once, over shared-memory rings and over the socket adaptor.
+static void testCommunicatorsInThreads() {
+  const int n = 4;
+  const size_t count = 50000;
+  flagcxUniqueId id;
+  EXPECT(flagcxGetUniqueId(&id) == flagcxSuccess);
+  std::atomic<int> bad{0};
+  std::vector<std::thread> th;
+  for (int r = 0; r < n; ++r)
+    th.emplace_back([&, r] {
+      flagcxComm_t comm = nullptr;
+      if (flagcxCommInitRank(&comm, n, &id, r) != flagcxSuccess) { ++bad; return; }
+      std::vector<float> x(count), out(count);
+      for (size_t i = 0; i < count; ++i) x[i] = (float)(i % 7) + r;
+      if (flagcxAllReduce(x.data(), out.data(), count, flagcxFloat, flagcxSum, comm, nullptr) != flagcxSuccess) ++bad;
+      for (size_t i = 0; i < count; i += 97)
+        if (out[i] != (float)n * (float)(i % 7) + (float)(n * (n - 1) / 2)) { ++bad; break; }
+      const size_t per = count / n;
+      std::vector<float> a2a(per * n);
+      if (flagcxAlltoAll(x.data(), a2a.data(), per, flagcxFloat, comm, nullptr) != flagcxSuccess) ++bad;
+      for (int p = 0; p < n; ++p)
+        if (a2a[p * per + 5] != (float)((r * per + 5) % 7) + p) ++bad;
+      int next = (r + 1) % n, prev = (r + n - 1) % n;
+      std::vector<float> got(count);
+      if (flagcxGroupStart(comm) != flagcxSuccess) ++bad;
+      if (flagcxSend(x.data(), count, flagcxFloat, next, comm, nullptr) != flagcxSuccess) ++bad;
+      if (flagcxRecv(got.data(), count, flagcxFloat, prev, comm, nullptr) != flagcxSuccess) ++bad;
+      if (flagcxGroupEnd(comm) != flagcxSuccess) ++bad;
+      if (got[3] != 3.f + prev) ++bad;
+      if (flagcxBarrier(comm, nullptr) != flagcxSuccess) ++bad;
+      if (flagcxCommDestroy(comm) != flagcxSuccess) ++bad;
+    });
+  for (auto &t : th) t.join();
+  EXPECT(bad.load() == 0);
+}
+
 static void testSocketAdaptor() {
   const flagcxNetAdaptor_v1 *net = flagcxGetNetAdaptor();
   EXPECT(net && std::string(net->name) == "socket");
@@ -257,6 +294,7 @@ int main() {
   testHostReduce();
   testSocketAdaptor();
   testBootstrapThreads();
+  testCommunicatorsInThreads();
   printf("%s: %d failure(s)\n", failures ? "FAILED" : "ok", failures);
   return failures;
 }

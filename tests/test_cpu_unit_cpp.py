@@ -43,7 +43,8 @@ def test_cpp_unit_tests_under_sanitizers(tmp_path, kind, flags):
     # the static CUDA runtime keeps process-lifetime allocations; leaks are not what this run is for
     env = dict(os.environ, FLAGCX_DEBUG="WARN", ASAN_OPTIONS="detect_leaks=0:abort_on_error=0",
                UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1", TSAN_OPTIONS="halt_on_error=0")
-    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    for needle in ("ERROR: AddressSanitizer", "runtime error", "WARNING: ThreadSanitizer"):
-        assert needle not in res.stderr, res.stderr[-3000:]
+    for shm in ("1", "0"):  # host ranks over shared-memory rings, then over the socket adaptor
+        res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=dict(env, FLAGCX_HOST_SHM=shm))
+        assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+        for needle in ("ERROR: AddressSanitizer", "runtime error", "WARNING: ThreadSanitizer"):
+            assert needle not in res.stderr, res.stderr[-3000:]
