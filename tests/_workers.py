@@ -674,3 +674,36 @@ def gpu_buffers_over_sockets(rank, n, uid):
     comm.barrier()
     comm.destroy()
     return worst
+
+
+# ---------------------------------------------------------------------------
+# sequence / context parallelism
+# ---------------------------------------------------------------------------
+def sp_ulysses_and_ring(rank, n, uid, S, H, D):
+    """Ulysses re-sharding and ring attention on CPU tensors against full attention."""
+    import torch
+    from flagcx_b200.parallel.sp import Ulysses, ring_attention
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(S, H, D, generator=g) for _ in range(3))
+    s = S // n
+    mine = slice(rank * s, (rank + 1) * s)
+    out = {}
+    u = Ulysses(comm)
+    heads = u.seq_to_heads(q[mine].contiguous())
+    h = H // n
+    out["seq_to_heads"] = float((heads - q[:, rank * h:(rank + 1) * h]).abs().max())
+    out["roundtrip"] = float((u.heads_to_seq(heads) - q[mine]).abs().max())
+
+    def full_attention(causal):
+        sc = torch.einsum("shd,thd->hst", q, k) / D ** 0.5
+        if causal:
+            sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), -float("inf"))
+        return torch.einsum("hst,thd->shd", sc.softmax(-1), v)
+
+    for causal in (False, True):
+        got = ring_attention(comm, q[mine].contiguous(), k[mine].contiguous(), v[mine].contiguous(), causal=causal)
+        out[f"ring_causal{int(causal)}"] = float((got - full_attention(causal)[mine]).abs().max())
+    comm.barrier()
+    comm.destroy()
+    return out
