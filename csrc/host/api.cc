@@ -262,20 +262,31 @@ flagcxResult_t flagcxMemFree(void *ptr, flagcxMemAllocator_t) {
   return flagcxSuccess;
 }
 
-// Local registration is bookkeeping only: peers learn about a buffer at window
-// registration.  The handle records the range for flagcxCommDeregister.
+// Local (non-collective) registration: exports the allocation to the peers ahead of its
+// first use, which a collective would otherwise do on the fly (reg_cache.h).  Memory that
+// cannot be exported is accepted too; collectives then copy through a stand-in.
 struct RegHandle { void *buf; size_t size; };
 
 flagcxResult_t flagcxCommRegister(const flagcxComm_t comm, void *buff, size_t size, void **handle,
                                   flagcxMemAllocator_t) {
   FCX_COMMCHECK(comm);
   if (!buff || !handle) return flagcxInvalidArgument;
+  if (comm->exportUserBuffers && comm->reg && !comm->windows.find(buff, size ? size : 1)) {
+    void *va[FLAGCX_MAX_RANKS];
+    comm->reg->lookup(buff, size ? size : 1, va);
+  }
   *handle = new RegHandle{buff, size};
   return flagcxSuccess;
 }
 flagcxResult_t flagcxCommDeregister(const flagcxComm_t comm, void *handle, flagcxMemAllocator_t) {
   FCX_COMMCHECK(comm);
-  delete (RegHandle *)handle;
+  RegHandle *h = (RegHandle *)handle;
+  if (h && comm->reg) {
+    // nobody may still be reading the allocation through its mappings
+    if (comm->devicePath) { cudaSetDevice(comm->cudaDev); cudaDeviceSynchronize(); }
+    comm->reg->forget(h->buf);
+  }
+  delete h;
   return flagcxSuccess;
 }
 
@@ -821,6 +832,22 @@ flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOp
   out->lastAlgo = s.lastAlgo;
   out->lastCtas = s.lastCtas;
   out->lastMs = s.lastMs;
+  return flagcxSuccess;
+}
+flagcxResult_t flagcxCommUserBufferStats(flagcxComm_t comm, flagcxUserBufferStats_t *out) {
+  FCX_COMMCHECK(comm);
+  if (!out) return flagcxInvalidArgument;
+  memset(out, 0, sizeof *out);
+  out->enabled = comm->exportUserBuffers ? 1 : 0;
+  if (comm->reg) {
+    RegCache::Counters k = comm->reg->counters();
+    out->hits = k.hits;
+    out->exports = k.exports;
+    out->refused = k.refused;
+    out->stale = k.stale;
+    out->peerOpened = k.opened;
+    out->peerClosed = k.closed;
+  }
   return flagcxSuccess;
 }
 flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes) {

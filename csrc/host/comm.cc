@@ -29,6 +29,7 @@ FCX_PARAM(VmmEnable, "VMM_ENABLE", 1)
 FCX_PARAM(NvlsEnable, "NVLS_ENABLE", 0)
 FCX_PARAM(WatchdogMs, "WATCHDOG_MS", 200)
 FCX_PARAM(P2pSlotBytes, "P2P_SLOT_BYTES", 4ll << 20)
+FCX_PARAM(UserBufferExport, "USER_BUFFER_EXPORT", 1)
 
 // ---------------------------------------------------------------------------
 // window registry
@@ -89,6 +90,8 @@ SyncLayout makeLayout() {
   off += (size_t)FLAGCX_MAX_RANKS * FLAGCX_P2P_CTAS * sizeof(uint64_t);
   l.p2pDoneOff = off;
   off += (size_t)FLAGCX_MAX_RANKS * FLAGCX_P2P_CTAS * sizeof(uint64_t);
+  l.ptrPadOff = off;
+  off += (size_t)FLAGCX_PTRPAD_WORDS * sizeof(uint64_t);
   off = alignUp(off, 1 << 16);
   l.zeroedBytes = off;
   l.stagingOff = off;
@@ -283,7 +286,13 @@ flagcxResult_t windowRegister(flagcxComm *c, void *buff, size_t size, int flags,
       w->peer[p] = (char *)opened + ex[p].offset;
     }
   }
-  FCXCHECK(c->bootstrap->barrier());
+  {
+    // where every rank mapped every other rank's copy: row p of the table is rank p's view
+    std::vector<void *> table((size_t)n * FLAGCX_MAX_RANKS, nullptr);
+    for (int p = 0; p < n; ++p) table[(size_t)me * FLAGCX_MAX_RANKS + p] = w->peer[p];
+    FCXCHECK(c->bootstrap->allGather(table.data(), sizeof(void *) * FLAGCX_MAX_RANKS));
+    for (int p = 0; p < n; ++p) w->selfAt[p] = table[(size_t)p * FLAGCX_MAX_RANKS + me];
+  }
   c->windows.add(w.get());
   FCX_INFO(SUB_REG, "rank %d registered window %p (%zu bytes, %s%s)", me, buff, size,
            mine.method == 0 ? "vmm" : "ipc", w->mc ? ", multicast" : "");
@@ -336,8 +345,30 @@ static flagcxResult_t setupDeviceWorld(flagcxComm *c, const std::vector<PeerInfo
   fillDevComm(c);
   c->tuner.reset(new Tuner());
   FCXCHECK(c->tuner->init(c));
-  FCX_INFO(SUB_INIT, "rank %d: device path over NVLink, %d ranks, staging %zu MiB, nvls %d", c->rank, n,
-           c->layout.stagingBytes >> 20, (int)c->nvls);
+  // registration service for user buffers: every rank must have one, or nobody uses it
+  {
+    std::vector<int32_t> up(n, 0);
+    if (n > 1 && readParam("USER_BUFFER_EXPORT", paramUserBufferExport()) != 0) {
+      c->reg.reset(new RegCache());
+      up[c->rank] = c->reg->start(c->bootstrap->nonce(), c->rank, n, cudaRegBackend(c->cudaDev)) == flagcxSuccess;
+    }
+    FCXCHECK(c->bootstrap->allGather(up.data(), sizeof(int32_t)));
+    bool all = true;
+    for (int v : up) all &= v != 0;
+    if (all) {
+      // open one small allocation at every peer now, while no kernel is running: the first
+      // inter-process mapping between two devices also sets up their peer access
+      void *va[FLAGCX_MAX_RANKS];
+      up.assign(n, 0);
+      up[c->rank] = c->reg->lookup(c->localSync, 8, va) ? 1 : 0;
+      FCXCHECK(c->bootstrap->allGather(up.data(), sizeof(int32_t)));
+      for (int v : up) all &= v != 0;
+    }
+    c->exportUserBuffers = all;
+    if (!all && c->reg) { c->reg->stop(); c->reg.reset(); }
+  }
+  FCX_INFO(SUB_INIT, "rank %d: device path over NVLink, %d ranks, staging %zu MiB, nvls %d, user-buffer export %d",
+           c->rank, n, c->layout.stagingBytes >> 20, (int)c->nvls, (int)c->exportUserBuffers);
   return flagcxSuccess;
 }
 
@@ -450,6 +481,15 @@ flagcxResult_t commDestroy(flagcxComm *c) {
     cudaDeviceSynchronize();
     // Peers may still be inside a kernel that touches our memory: leave together.
     if (!c->aborted && c->asyncError.load() == flagcxSuccess) c->bootstrap->barrier();
+    if (c->reg) {
+      // unmap what this rank opened for its peers, then meet again: nobody frees an
+      // allocation that a peer still has mapped
+      c->reg->stop();
+      c->reg.reset();
+      if (!c->aborted && c->asyncError.load() == flagcxSuccess) c->bootstrap->barrier();
+    }
+    for (void *&b : c->bounce)
+      if (b) { cudaFree(b); b = nullptr; }
     for (Window *w : c->windows.all())
       if (!w->internal) windowDeregister(c, w);
     void *internalBase = c->internalWin ? c->internalWin->local : nullptr;

@@ -21,6 +21,7 @@
 #include "cuda_rt.h"
 #include "flagcx.h"
 #include "flagcx_device.cuh"
+#include "reg_cache.h"
 #include "../kernels/coll_args.h"
 
 struct flagcxStream {
@@ -40,6 +41,7 @@ struct Window {
   void *local = nullptr;
   size_t size = 0;
   void *peer[FLAGCX_MAX_RANKS] = {};
+  void *selfAt[FLAGCX_MAX_RANKS] = {}; // this rank's copy as addressed by rank r (for published pointers)
   void *mc = nullptr;   // multicast alias (NVLS) or null
   int flags = 0;
   bool internal = false;
@@ -83,7 +85,7 @@ struct GroupOp {
 
 // Layout of the internal window of every rank (offsets are identical everywhere).
 struct SyncLayout {
-  size_t inboxOff, signalOff, metaOff, p2pReadyOff, p2pDoneOff, zeroedBytes;
+  size_t inboxOff, signalOff, metaOff, p2pReadyOff, p2pDoneOff, ptrPadOff, zeroedBytes;
   size_t stagingOff, stagingBytes;   // collectives on unregistered buffers
   size_t p2pStageOff, p2pSlotBytes;  // send/recv: FLAGCX_MAX_RANKS slots
   size_t total;
@@ -113,7 +115,14 @@ struct flagcxComm {
   flagcxDevStatus *status = nullptr; // pinned host page
   flagcxDevStatus *statusDev = nullptr; // device alias of the same page
   void *localSync = nullptr;       // epochs, shadows, counters (cudaMalloc)
-  uint64_t stageParity = 0;        // alternates the staging half for one-shot
+  // User buffers outside symmetric windows: exported to the peers on first use
+  // (reg_cache.h) and found by the peers' kernels through the run-time pointer
+  // exchange.  Off (legacy in-kernel staging) when any rank could not start the service.
+  std::unique_ptr<fcx::RegCache> reg;
+  bool exportUserBuffers = false;
+  uint64_t xchgSeq = 0;            // exchanging launches so far (same on every rank)
+  void *bounce[2] = {nullptr, nullptr}; // exportable stand-ins for buffers that are not (input, output)
+  size_t bounceBytes[2] = {0, 0};
   int winSeq = 0;                  // window registrations so far (same on every rank)
   unsigned int *putArrival = nullptr; // device word used by put kernels
   volatile uint64_t *rmaCounter = nullptr; // pinned: one-sided operations completed

@@ -350,6 +350,21 @@ flagcxResult_t addressRange(const void *p, void **base, size_t *size) {
   return flagcxSuccess;
 }
 
+flagcxResult_t allocationInfo(const void *p, void **base, size_t *size, uint64_t *id) {
+  Driver *d = driver();
+  if (!d->ok) return flagcxNotSupported;
+  CUdeviceptr b = 0;
+  size_t s = 0;
+  // quiet on failure: callers probe pointers that may not be device allocations
+  if (d->p_cuMemGetAddressRange(&b, &s, (CUdeviceptr)p) != CUDA_SUCCESS) return flagcxInvalidArgument;
+  unsigned long long bid = 0;
+  if (d->p_cuPointerGetAttribute(&bid, CU_POINTER_ATTRIBUTE_BUFFER_ID, b) != CUDA_SUCCESS) return flagcxInvalidArgument;
+  *base = (void *)b;
+  *size = s;
+  *id = bid;
+  return flagcxSuccess;
+}
+
 flagcxResult_t tensorMap2dBf16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint32_t boxRows,
                                uint32_t boxCols) {
   Driver *d = driver();

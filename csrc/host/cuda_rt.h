@@ -86,6 +86,9 @@ enum PtrKind { kPtrHost = 0, kPtrDevice = 1, kPtrManaged = 2 };
 PtrKind classify(const void *p, int *dev);
 // Base and size of the driver allocation containing p.
 flagcxResult_t addressRange(const void *p, void **base, size_t *size);
+// The same plus the driver's id of that allocation, which is never handed out twice:
+// tells a freed-and-reallocated address from the allocation seen before.
+flagcxResult_t allocationInfo(const void *p, void **base, size_t *size, uint64_t *id);
 
 // Tensor map for TMA tile loads of a row-major bf16 matrix [rows, cols] (cols
 // contiguous), box of boxRows x boxCols elements, 128-byte swizzle.  boxCols * 2 must

@@ -54,6 +54,108 @@ void setOut(flagcxComm *c, CollArgs &a, const BufView &v, void *local, size_t ex
     a.out[c->rank] = (char *)local + extraOff;
   }
 }
+// ---- user buffers outside windows ------------------------------------------------------
+// How the peers' kernels reach a buffer of this rank.
+enum Reach {
+  kReachNone = 0, // they cannot: the legacy path stages it through the internal window
+  kReachWindow,   // inside a symmetric window: every address is known on the host
+  kReachEmu,      // emulated world: the launcher fills in the other ranks' addresses
+  kReachExport    // exported on demand (reg_cache.h); peers learn the address inside the kernel
+};
+
+struct UserBuf {
+  Reach reach = kReachNone;
+  BufView view;
+  void *user = nullptr;  // what the caller passed
+  void *local = nullptr; // what the local kernel uses: the same, or an exportable stand-in
+  size_t bytes = 0;
+  void *peerVa[FLAGCX_MAX_RANKS] = {};
+  bool visible() const { return reach != kReachNone; }
+  bool bounced() const { return local != user; }
+};
+
+// A device allocation of at least `bytes` that can be exported (cudaMalloc memory),
+// kept per communicator and direction.
+flagcxResult_t bounceBuffer(flagcxComm *c, int which, size_t bytes, void **out) {
+  if (c->bounceBytes[which] < bytes) {
+    if (c->bounce[which]) {
+      FCX_CUDACHECK(cudaDeviceSynchronize()); // earlier collectives may still use it, peers included
+      c->reg->forget(c->bounce[which]);
+      FCX_CUDACHECK(cudaFree(c->bounce[which]));
+      c->bounce[which] = nullptr;
+      c->bounceBytes[which] = 0;
+    }
+    size_t want = alignUp(bytes, (size_t)2 << 20);
+    FCX_CUDACHECK(cudaMalloc(&c->bounce[which], want));
+    c->bounceBytes[which] = want;
+    FCX_INFO(SUB_REG, "rank %d: %zu MiB stand-in for %s buffers that cannot be exported", c->rank, want >> 20,
+             which ? "output" : "input");
+  }
+  *out = c->bounce[which];
+  return flagcxSuccess;
+}
+
+// Finds out how `p` is reachable.  With on-demand export enabled this never answers
+// kReachNone for a non-null buffer: a buffer that cannot be exported (memory that is
+// not a cudaMalloc block) is replaced by an exportable stand-in, filled from it
+// (inputs) on `stream` here or copied back (outputs) by finishOut().
+flagcxResult_t resolve(flagcxComm *c, const void *p, size_t bytes, int which, cudaStream_t stream, UserBuf *u) {
+  *u = UserBuf();
+  u->user = u->local = const_cast<void *>(p);
+  u->bytes = bytes;
+  if (!p) return flagcxSuccess;
+  if (c->emu) {
+    if (getEnv("FLAGCX_EMU_FORCE_STAGING")) return flagcxSuccess;
+    if (getEnv("FLAGCX_EMU_EXCHANGE")) { // one address space: every rank sees the buffer where it is
+      u->reach = kReachExport;
+      for (int r = 0; r < c->nranks; ++r) u->peerVa[r] = u->local;
+    } else {
+      u->reach = kReachEmu;
+    }
+    return flagcxSuccess;
+  }
+  u->view = viewOf(c, p, bytes);
+  if (u->view.visible()) { u->reach = kReachWindow; return flagcxSuccess; }
+  if (!c->exportUserBuffers || c->nranks == 1) return flagcxSuccess;
+  if (c->reg->lookup(p, bytes ? bytes : 1, u->peerVa)) { u->reach = kReachExport; return flagcxSuccess; }
+  void *b = nullptr;
+  FCXCHECK(bounceBuffer(c, which, bytes, &b));
+  if (!c->reg->lookup(b, bytes ? bytes : 1, u->peerVa)) {
+    FCX_WARN("rank %d: neither the user buffer %p nor a stand-in could be exported to the peers", c->rank, p);
+    return flagcxUnhandledDeviceError;
+  }
+  u->local = b;
+  u->reach = kReachExport;
+  if (which == 0 && bytes) FCX_CUDACHECK(cudaMemcpyAsync(b, p, bytes, cudaMemcpyDeviceToDevice, stream));
+  return flagcxSuccess;
+}
+
+flagcxResult_t finishOut(const UserBuf &u, cudaStream_t stream) {
+  if (u.bounced() && u.bytes) FCX_CUDACHECK(cudaMemcpyAsync(u.user, u.local, u.bytes, cudaMemcpyDeviceToDevice, stream));
+  return flagcxSuccess;
+}
+
+void applyIn(flagcxComm *c, CollArgs &a, const UserBuf &u, size_t extraOff = 0) {
+  if (u.reach == kReachWindow) { setIn(c, a, u.view, u.user, extraOff); return; }
+  setIn(c, a, BufView(), u.local, extraOff);
+  if (u.reach == kReachExport) {
+    a.xchg |= kXchgIn;
+    for (int p = 0; p < c->nranks; ++p) a.pubIn[p] = (const char *)u.peerVa[p] + extraOff;
+  }
+}
+void applyOut(flagcxComm *c, CollArgs &a, const UserBuf &u, size_t extraOff = 0) {
+  if (u.reach == kReachWindow) { setOut(c, a, u.view, u.user, extraOff); return; }
+  setOut(c, a, BufView(), u.local, extraOff);
+  if (u.reach == kReachExport) {
+    a.xchg |= kXchgOut;
+    for (int p = 0; p < c->nranks; ++p) a.pubOut[p] = (char *)u.peerVa[p] + extraOff;
+  }
+}
+// The output is only written by the local kernel: no peer needs its address.
+void applyOutLocal(flagcxComm *c, CollArgs &a, const UserBuf &u, size_t extraOff = 0) {
+  setOut(c, a, BufView(), u.local, extraOff);
+}
+
 // Staging region [off, off+...) of every rank.
 void setInStage(flagcxComm *c, CollArgs &a, size_t off) {
   BufView v{c->internalWin, c->layout.stagingOff + off};
@@ -71,8 +173,10 @@ void initArgs(flagcxComm *c, CollArgs &a, int kind, flagcxDataType_t dt) {
   a.elemSize = (int)getFlagcxDataTypeSize(dt);
   a.scale = 1.0f;
   a.flags = kFlagBeginBarrier | kFlagEndBarrier;
-  for (int p = 0; p < c->nranks; ++p)
+  for (int p = 0; p < c->nranks; ++p) {
     a.meta[p] = (unsigned long long *)((char *)c->internalWin->peer[p] + c->layout.metaOff);
+    a.ptrPad[p] = (unsigned long long *)((char *)c->internalWin->peer[p] + c->layout.ptrPadOff);
+  }
 }
 
 // Push kinds whose blocks are large and 16-byte aligned move through the bulk-copy
@@ -82,7 +186,7 @@ int bulkStageFor(flagcxComm *c, const CollArgs &a) {
   if (a.kind != kAllGatherPush && a.kind != kAllToAllPush && a.kind != kBroadcastPush) return 0;
   // measured on B200 pairs: the engine wins (about 670 against 590 GB/s per direction)
   // once a rank sends some tens of MB; below that its start-up costs more than it saves
-  static const int64_t enable = readParam("BULK_COPY", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20);
+  const int64_t enable = readParam("BULK_COPY", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20);
   const size_t blk = a.count * (size_t)a.elemSize;
   if (!enable || blk * (size_t)std::max(1, c->nranks - 1) < (size_t)minBytes || blk % 16) return 0;
   uintptr_t bits = (uintptr_t)a.in[c->rank] | a.inStride | a.outStride;
@@ -99,8 +203,8 @@ int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
   if (a.dtype != flagcxFloat32 && a.dtype != flagcxBfloat16 && a.dtype != flagcxFloat16) return 0;
   // measured on 8 B200s: reduce-scatter gains from 64 MB of peer input on (667 against 606 GB/s
   // at 4 GiB), the two-shot all-reduce only from about 400 MB on
-  static const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20),
-                       minAllReduce = readParam("BULK_ALLREDUCE_MIN_BYTES", 400 << 20);
+  const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20),
+                minAllReduce = readParam("BULK_ALLREDUCE_MIN_BYTES", 400 << 20);
   const size_t es = (size_t)a.elemSize, bytes = a.count * es;
   if (!enable || bytes % 16) return 0;
   const size_t slice = a.kind == kReduceScatter ? a.count : sliceElems(a.count, n, es);
@@ -111,26 +215,28 @@ int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
   return (bits & 15) ? 0 : 1;
 }
 
-flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a, int nCtas, cudaStream_t stream) {
+flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a0, int nCtas, cudaStream_t stream) {
   nCtas = std::max(1, std::min(nCtas, FLAGCX_COLL_BARRIER_SLOTS));
+  CollArgs a = a0;
+  // every rank issues the same sequence of collective launches, so the parity agrees
+  // whether or not a given rank exchanges pointers in a given launch
+  a.xchgParity = (uint32_t)(c->xchgSeq++ & 1);
+  if (a.xchg) a.flags |= kFlagBeginBarrier | kFlagEndBarrier;
+  if (family == kFamCopy) {
+    a.bulkStage = bulkStageFor(c, a);
+    a.bulkDepth = readParam("BULK_STAGES", 8) >= 12 ? 12 : 8;
+  } else if (family == kFamReduce) {
+    a.bulkStage = bulkReduceFor(c, a);
+  }
   if (c->emu) return emuSubmit(c, family, &a, nullptr, nCtas, stream);
   LaunchCtx lc;
   lc.comm = &c->dev;
   lc.stream = stream;
   lc.nCtas = nCtas;
   cudaError_t e;
-  if (family == kFamCopy) {
-    CollArgs b = a;
-    b.bulkStage = bulkStageFor(c, a);
-    b.bulkDepth = readParam("BULK_STAGES", 8) >= 12 ? 12 : 8;
-    e = launchCopyKernel(lc, b);
-  } else if (family == kFamReduce) {
-    CollArgs b = a;
-    b.bulkStage = bulkReduceFor(c, a);
-    e = launchReduceKernel(lc, b, c->nranks);
-  } else {
-    e = launchNvlsKernel(lc, a);
-  }
+  if (family == kFamCopy) e = launchCopyKernel(lc, a);
+  else if (family == kFamReduce) e = launchReduceKernel(lc, a, c->nranks);
+  else e = launchNvlsKernel(lc, a);
   if (e != cudaSuccess) {
     FCX_WARN("kernel launch failed: %s", cudaGetErrorString(e));
     return flagcxUnhandledDeviceError;
@@ -202,8 +308,11 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   FCXCHECK(setReduceEpilogue(c, a, rq));
   const size_t es = a.elemSize, oes = outElemSize(a);
   const size_t count = rq.count;
-  BufView vin = viewOf(c, rq.send, count * es), vout = viewOf(c, rq.recv, count * oes);
-  const bool inVis = vin.visible() || emuVisible(c), outVis = vout.visible() || emuVisible(c);
+  UserBuf uin, uout;
+  FCXCHECK(resolve(c, rq.send, count * es, 0, stream, &uin));
+  if (rq.send == rq.recv) uout = uin; // in place stays in place, stand-in included
+  else FCXCHECK(resolve(c, rq.recv, count * oes, 1, stream, &uout));
+  const bool inVis = uin.visible(), outVis = uout.visible();
   const bool nvlsOk = nvlsEligible(c, rq, count);
   TuneChoice ch = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, inVis && outVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
@@ -212,42 +321,42 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       algo != FLAGCX_ALGO_NVLS_TWOSHOT)
     algo = FLAGCX_ALGO_TWOSHOT;
   // one-shot writes its output while peers may still read the same addresses
-  if (algo == FLAGCX_ALGO_ONESHOT && rq.send == rq.recv && inVis) algo = FLAGCX_ALGO_TWOSHOT;
+  if (algo == FLAGCX_ALGO_ONESHOT && uin.local == uout.local && inVis) algo = FLAGCX_ALGO_TWOSHOT;
   if (n == 1) algo = FLAGCX_ALGO_ONESHOT;
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpAllReduce, count * es, algo, nCtas);
   const size_t S = c->layout.stagingBytes, half = S / 2;
   const bool nvlsAlgo = algo == FLAGCX_ALGO_NVLS_ONESHOT || algo == FLAGCX_ALGO_NVLS_TWOSHOT;
   // multimem needs multicast aliases: windows bound at registration, else the staging
-  const bool inMc = vin.win && vin.win->mc, outMc = vout.win && vout.win->mc;
+  const bool inMc = uin.view.win && uin.view.win->mc, outMc = uout.view.win && uout.view.win->mc;
 
   if (algo == FLAGCX_ALGO_ONESHOT || algo == FLAGCX_ALGO_NVLS_ONESHOT) {
     a.kind = nvlsAlgo ? kAllReduceNvlsOneShot : kAllReduceOneShot;
     const bool direct = nvlsAlgo ? inMc : inVis;
     if (direct) {
       a.count = count;
-      setIn(c, a, vin, rq.send);
-      setOut(c, a, BufView(), rq.recv);
-      return launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream);
+      applyIn(c, a, uin);
+      applyOutLocal(c, a, uout);
+      FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
+      return finishOut(uout, stream);
     }
-    // staged input, alternating halves: the barrier of the next call proves that
-    // every peer finished reading this half, so no trailing barrier is needed
-    size_t chunk = half / es / 16 * 16;
+    // Staged input.  The closing barrier stays: the next collective, whatever its kind,
+    // overwrites the staging from offset 0 on, and must not start before every peer has
+    // finished reading this one's.
+    size_t chunk = S / es / 16 * 16;
     for (size_t off = 0; off < count || off == 0; off += chunk) {
       size_t cnt = std::min(chunk, count - off);
       a.count = cnt;
-      setInStage(c, a, (c->stageParity & 1) * half);
-      c->stageParity++;
-      a.userIn = (const char *)rq.send + off * es;
+      setInStage(c, a, 0);
+      a.userIn = (const char *)uin.local + off * es;
       a.nInBlocks = 1;
       a.inBlockBytes = cnt * es;
-      setOut(c, a, BufView(), rq.recv, off * oes);
+      applyOutLocal(c, a, uout, off * oes);
       a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
-      a.flags = kFlagBeginBarrier;
       FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
       if (count == 0) break;
     }
-    return flagcxSuccess;
+    return finishOut(uout, stream);
   }
 
   // two-shot
@@ -255,32 +364,34 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   const bool inDirect = nvlsAlgo ? inMc : inVis, outDirect = nvlsAlgo ? outMc : outVis;
   if (inDirect && outDirect) {
     a.count = count;
-    setIn(c, a, vin, rq.send);
-    setOut(c, a, vout, rq.recv);
-    return launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream);
+    applyIn(c, a, uin);
+    applyOut(c, a, uout);
+    FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
+    return finishOut(uout, stream);
   }
   size_t chunk = half / std::max(es, oes) / (16 * (size_t)n) * (16 * (size_t)n);
   for (size_t off = 0; off < count || off == 0; off += chunk) {
     size_t cnt = std::min(chunk, count - off);
     a.count = cnt;
+    a.xchg = 0;
     size_t slice = sliceElems(cnt, n, es);
     if (inDirect) {
-      setIn(c, a, vin, rq.send, off * es);
+      applyIn(c, a, uin, off * es);
       a.userIn = nullptr;
     } else {
       setInStage(c, a, 0);
-      a.userIn = (const char *)rq.send + off * es;
+      a.userIn = (const char *)uin.local + off * es;
       a.nInBlocks = n;
       a.inBlockBytes = slice * es;
       a.userInStride = slice * es;
       a.inTotalBytes = cnt * es;
     }
     if (outDirect) {
-      setOut(c, a, vout, rq.recv, off * oes);
+      applyOut(c, a, uout, off * oes);
       a.userOut = nullptr;
     } else {
       setOutStage(c, a, half);
-      a.userOut = (char *)rq.recv + off * oes;
+      a.userOut = (char *)uout.local + off * oes;
       a.nOutBlocks = n;
       a.outBlockBytes = slice * oes;
       a.userOutStride = slice * oes;
@@ -290,7 +401,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
     FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
     if (count == 0) break;
   }
-  return flagcxSuccess;
+  return finishOut(uout, stream);
 }
 
 flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
@@ -299,9 +410,10 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   initArgs(c, a, kReduceScatter, rq.dtype);
   FCXCHECK(setReduceEpilogue(c, a, rq));
   const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
-  BufView vin = viewOf(c, rq.send, count * es * n);
-  const bool inVis = vin.visible() || emuVisible(c);
-  const bool nvlsOk = nvlsEligible(c, rq, count) && vin.win && vin.win->mc;
+  UserBuf uin;
+  FCXCHECK(resolve(c, rq.send, count * es * n, 0, stream, &uin));
+  const bool inVis = uin.visible();
+  const bool nvlsOk = nvlsEligible(c, rq, count) && uin.view.win && uin.view.win->mc;
   TuneChoice ch = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, inVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PULL;
@@ -311,7 +423,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
     a.kind = algo == FLAGCX_ALGO_NVLS ? kReduceScatterNvls : kReduceScatter;
     a.count = count;
     a.inStride = count * es;
-    setIn(c, a, vin, rq.send);
+    applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
     return launch(c, algo == FLAGCX_ALGO_NVLS ? kFamNvls : kFamReduce, a, nCtas, stream);
   }
@@ -341,14 +453,15 @@ flagcxResult_t reduceToRoot(flagcxComm *c, const DeviceCollRequest &rq, cudaStre
   FCXCHECK(setReduceEpilogue(c, a, rq));
   a.root = rq.root;
   const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
-  BufView vin = viewOf(c, rq.send, count * es);
-  const bool inVis = vin.visible() || emuVisible(c);
+  UserBuf uin;
+  FCXCHECK(resolve(c, rq.send, count * es, 0, stream, &uin));
+  const bool inVis = uin.visible();
   TuneChoice ch = c->tuner->choose(flagcxCommOpReduce, count * es, n, inVis, false);
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpReduce, count * es, FLAGCX_ALGO_PULL, nCtas);
   if (inVis) {
     a.count = count;
-    setIn(c, a, vin, rq.send);
+    applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
     return launch(c, kFamReduce, a, nCtas, stream);
   }
@@ -369,12 +482,6 @@ flagcxResult_t reduceToRoot(flagcxComm *c, const DeviceCollRequest &rq, cudaStre
 }
 
 // ---- copy family: everything in bytes -----------------------------------------------
-struct CopyPlan {
-  flagcxCommOp_t op;
-  int pushKind, pullKind; // -1: not available
-  bool stagedBlocksPerRank; // staging holds n blocks (scatter, alltoall) instead of one
-};
-
 flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
   const int n = c->nranks, me = c->rank;
   const size_t es = getFlagcxDataTypeSize(rq.dtype);
@@ -401,11 +508,35 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   // argument is meaningful, so visibility is judged on the argument every rank has.
   const bool sendEverywhere = rq.op != flagcxCommOpBroadcast && rq.op != flagcxCommOpScatter;
   const bool recvEverywhere = rq.op != flagcxCommOpGather;
-  BufView vin = sendEverywhere ? viewOf(c, rq.send, sendBytes) : BufView();
-  BufView vout = recvEverywhere ? viewOf(c, rq.recv, recvBytes) : BufView();
-  const bool inVis = vin.visible() || (emuVisible(c) && sendEverywhere);
-  const bool outVis = vout.visible() || (emuVisible(c) && recvEverywhere);
-  const bool nvlsOk = rq.op == flagcxCommOpAllGather && c->nvls && !c->emu && vout.win && vout.win->mc &&
+  const bool iAmRoot = me == rq.root;
+  UserBuf uin, uout;
+  if (sendEverywhere) FCXCHECK(resolve(c, rq.send, sendBytes, 0, stream, &uin));
+  if (recvEverywhere) FCXCHECK(resolve(c, rq.recv, recvBytes, 1, stream, &uout));
+  bool inVis = uin.visible(), outVis = uout.visible();
+  // Scatter has no argument that every rank owns: with run-time pointer exchange the
+  // root alone publishes its input and the others learn it.
+  const bool exchanging = c->emu ? getEnv("FLAGCX_EMU_EXCHANGE") != nullptr : c->exportUserBuffers;
+  bool scatterExchange = false;
+  if (rq.op == flagcxCommOpScatter && exchanging && n > 1) {
+    if (iAmRoot) {
+      FCXCHECK(resolve(c, rq.send, sendBytes, 0, stream, &uin));
+      if (uin.reach == kReachWindow) { // peers passed no pointer they could look up: tell them
+        Window *w = uin.view.win;
+        bool known = true;
+        for (int p = 0; p < n; ++p) known &= w->selfAt[p] != nullptr;
+        if (known) {
+          for (int p = 0; p < n; ++p) uin.peerVa[p] = (char *)w->selfAt[p] + uin.view.off;
+          uin.reach = kReachExport;
+        }
+      }
+      scatterExchange = uin.reach == kReachExport;
+      if (!scatterExchange) { FCX_WARN("scatter: the root's buffer cannot be published to the peers"); return flagcxInternalError; }
+    } else {
+      scatterExchange = true;
+    }
+    inVis = true;
+  }
+  const bool nvlsOk = rq.op == flagcxCommOpAllGather && c->nvls && !c->emu && uout.view.win && uout.view.win->mc &&
                       blk % 16 == 0 && aligned16(rq.send);
   TuneChoice ch = c->tuner->choose(rq.op, std::max(sendBytes, recvBytes), n, inVis || outVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
@@ -423,7 +554,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
     a.count = blk / 4;
     a.outStride = blk;
     setIn(c, a, BufView(), rq.send);
-    setOut(c, a, vout, rq.recv);
+    setOut(c, a, uout.view, rq.recv);
     return launch(c, kFamNvls, a, nCtas, stream);
   }
   if (algo == FLAGCX_ALGO_PUSH) {
@@ -431,23 +562,31 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
     a.count = blk;
     a.inStride = blk;
     a.outStride = blk;
+    // the input is only read locally: a stand-in is not needed for it
     setIn(c, a, BufView(), rq.send);
-    setOut(c, a, vout, rq.recv);
-    return launch(c, kFamCopy, a, nCtas, stream);
+    applyOut(c, a, uout);
+    FCXCHECK(launch(c, kFamCopy, a, nCtas, stream));
+    return finishOut(uout, stream);
   }
   a.kind = pullKind;
   if (inVis) {
     a.count = blk;
     a.inStride = blk;
     a.outStride = blk;
-    setIn(c, a, vin, rq.send);
+    if (scatterExchange) {
+      setIn(c, a, BufView(), iAmRoot ? uin.local : nullptr);
+      a.xchg |= kXchgIn;
+      for (int p = 0; p < n; ++p) a.pubIn[p] = iAmRoot ? (const char *)uin.peerVa[p] : nullptr;
+    } else {
+      applyIn(c, a, uin);
+    }
     setOut(c, a, BufView(), rq.recv);
     return launch(c, kFamCopy, a, nCtas, stream);
   }
   // staged input
   const size_t S = c->layout.stagingBytes;
   size_t chunk = (nBlocksIn ? S / n : S) / 16 * 16;
-  const bool iStage = !(rq.op == flagcxCommOpBroadcast || rq.op == flagcxCommOpScatter) || me == rq.root;
+  const bool iStage = !(rq.op == flagcxCommOpBroadcast || rq.op == flagcxCommOpScatter) || iAmRoot;
   for (size_t off = 0; off < blk || off == 0; off += chunk) {
     size_t len = std::min(chunk, blk - off);
     a.count = len;
@@ -466,7 +605,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
 }
 
 flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
-  const int n = c->nranks, me = c->rank;
+  const int n = c->nranks;
   const size_t es = getFlagcxDataTypeSize(rq.dtype);
   size_t sendSpan = 0, recvSpan = 0, total = 0;
   for (int p = 0; p < n; ++p) {
@@ -474,9 +613,13 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
     recvSpan = std::max(recvSpan, (rq.recvDispls[p] + rq.recvCounts[p]) * es);
     total += rq.sendCounts[p] * es;
   }
-  BufView vin = viewOf(c, rq.send, sendSpan);
-  const bool inVis = vin.visible() || emuVisible(c);
-  if (inVis) {
+  // Spans differ between ranks, so "is it inside a window / exportable" is decided on a
+  // property every rank shares: the communicator's mode.  A rank whose buffer cannot be
+  // exported gets a stand-in inside resolve().
+  UserBuf uin;
+  FCXCHECK(resolve(c, rq.send, sendSpan, 0, stream, &uin));
+  if (!rq.send && c->exportUserBuffers) uin.reach = kReachExport; // nothing to send: publish a null pointer
+  if (uin.visible()) {
     CollArgs a;
     initArgs(c, a, kAllToAllvPull, rq.dtype);
     for (int p = 0; p < n; ++p) {
@@ -485,7 +628,7 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       a.recvCounts[p] = rq.recvCounts[p];
       a.recvDispls[p] = rq.recvDispls[p];
     }
-    setIn(c, a, vin, rq.send);
+    applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
     TuneChoice ch = c->tuner->choose(flagcxCommOpAlltoAllv, total, n, true, false);
     const int nCtas = pickCtas(c, rq, ch);
@@ -499,7 +642,6 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
                            rq.sendCounts[p] * es, stream});
     c->groupOps.push_back({false, p, (char *)rq.recv + rq.recvDispls[p] * es, rq.recvCounts[p] * es, stream});
   }
-  (void)me;
   return deviceGroupLaunch(c);
 }
 

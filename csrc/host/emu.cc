@@ -109,6 +109,7 @@ flagcxResult_t emuWindowRegister(flagcxComm *c, void *buff, size_t size, int fla
   win->size = size;
   win->flags = flags;
   win->peer[c->rank] = buff;
+  for (int p = 0; p < c->nranks; ++p) win->selfAt[p] = buff; // one address space
   const int seq = c->winSeq++;
   for (flagcxComm *o : w->comms) {
     if (o == c) continue;
@@ -193,10 +194,12 @@ flagcxResult_t emuSubmit(flagcxComm *c, int family, const CollArgs *coll, const 
     for (int q = 0; q < n; ++q) {
       if (w->coll[q].kind != w->coll[0].kind) { FCX_WARN("emulated ranks chose different algorithms"); return flagcxInvalidUsage; }
       for (int p = 0; p < n; ++p) {
-        if (!w->coll[q].in[p]) w->coll[q].in[p] = w->coll[p].in[p];
-        if (!w->coll[q].out[p]) w->coll[q].out[p] = w->coll[p].out[p];
+        // a rank that exchanges pointers inside the kernel must get them from there
+        if (!w->coll[q].in[p] && !(w->coll[q].xchg & kXchgIn)) w->coll[q].in[p] = w->coll[p].in[p];
+        if (!w->coll[q].out[p] && !(w->coll[q].xchg & kXchgOut)) w->coll[q].out[p] = w->coll[p].out[p];
       }
     }
+    for (int q = 0; q < n; ++q) lc.emuBulk |= w->coll[q].bulkStage != 0;
     CollArgs *d = w->dColl + (size_t)slot * n;
     FCX_CUDACHECK(cudaMemcpyAsync(d, w->coll.data(), sizeof(CollArgs) * n, cudaMemcpyHostToDevice, stream));
     lc.emuArgs = d;

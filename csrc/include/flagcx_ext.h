@@ -79,6 +79,18 @@ flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOp
  * FLAGCX_NVTX=1 additionally opens an NVTX range around every collective. */
 flagcxResult_t flagcxCommTraceEnable(flagcxComm_t comm, int capacity);
 flagcxResult_t flagcxCommTraceDump(flagcxComm_t comm, const char *path);
+/* User buffers outside registered windows (ordinary cudaMalloc memory, e.g. PyTorch
+ * tensors) are exported to the peers the first time a collective meets them, one-sidedly
+ * and without staging copies afterwards; flagcxCommRegister does the same ahead of time.
+ * Counters of this rank: lookups served from the cache, allocations exported, allocations
+ * that could not be exported (they go through an exportable stand-in), stale entries
+ * replaced after the address was freed and reused, allocations of peers mapped / unmapped
+ * here.  enabled is 0 when FLAGCX_USER_BUFFER_EXPORT=0 or the service could not start. */
+typedef struct {
+  int enabled;
+  uint64_t hits, exports, refused, stale, peerOpened, peerClosed;
+} flagcxUserBufferStats_t;
+flagcxResult_t flagcxCommUserBufferStats(flagcxComm_t comm, flagcxUserBufferStats_t *out);
 /* 1 when collectives on device buffers run as NVLink kernels, 0 on the socket path. */
 flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes);
 flagcxResult_t flagcxCommHasMulticast(flagcxComm_t comm, int *yes);

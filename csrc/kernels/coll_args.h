@@ -31,6 +31,9 @@ enum CollKind : int {
   kAllReduceNvlsTwoShot, // multimem.ld_reduce own slice -> multimem.st to all
   kReduceScatterNvls,    // multimem.ld_reduce own block -> local output
   kAllGatherNvls,        // multimem.st own block to all
+  kAllReduceTwoShotCast, // reduce own slice into local 16-bit scratch, then pull all slices and widen to fp32
+  kLlAllReduce,          // small messages: data+flag stores into per-sender slots, no barrier
+  kLlAllGather,
   kNumCollKinds
 };
 
@@ -40,6 +43,14 @@ enum CollFlags : uint32_t {
 };
 
 enum OutMode : int { kOutSame = 0, kOutFloat = 1, kOutBf16 = 2 };
+
+// Which of a rank's buffers the kernel learns from its peers at run time
+// (CollArgs::xchg).  A rank whose buffer is not inside a symmetric window cannot know
+// on the host where its peers' buffers are; instead every rank tells each peer,
+// before the kernel's first barrier, where ITS buffer is in that peer's address space.
+enum XchgBits : uint32_t { kXchgIn = 1u << 0, kXchgOut = 1u << 1 };
+// Pointer pad of a rank (inside its internal window): [parity][cta slot][source rank][in,out].
+#define FLAGCX_PTRPAD_WORDS (2 * FLAGCX_COLL_BARRIER_SLOTS * FLAGCX_MAX_RANKS * 2)
 
 // Reduction operator as the kernels see it (flagcxAvg arrives as sum plus a scale).
 enum : int { kOpSum = 0, kOpProd = 1, kOpMax = 2, kOpMin = 3, kOpRuntime = -1 };
@@ -64,6 +75,20 @@ struct CollArgs {
   char *userOut;                    // if set: out[rank] is copied here after the last barrier
   const char *residual;             // optional: added to the result before the store
   unsigned long long *meta[FLAGCX_MAX_RANKS]; // per-rank pad of 2*FLAGCX_MAX_RANKS u64 (alltoallv)
+  // run-time pointer exchange (xchg != 0): pubIn[p] / pubOut[p] is this rank's input /
+  // output as rank p addresses it; ptrPad[p] is rank p's pointer pad as mapped here
+  const char *pubIn[FLAGCX_MAX_RANKS];
+  char *pubOut[FLAGCX_MAX_RANKS];
+  unsigned long long *ptrPad[FLAGCX_MAX_RANKS];
+  // aux[p]: a region of rank p's internal window as mapped here.  kAllReduceTwoShotCast:
+  // the 16-bit scratch that holds rank p's reduced slice.  LL kinds: rank p's slot area,
+  // laid out [parity][sender][llSlotBytes].
+  char *aux[FLAGCX_MAX_RANKS];
+  size_t llSlotBytes;
+  uint32_t llEpoch;    // value of the flags of this operation (never 0)
+  uint32_t llPad;
+  uint32_t xchg;       // XchgBits
+  uint32_t xchgParity; // alternates between consecutive exchanging launches of a communicator
   size_t count;        // elements: total (allreduce, reduce, broadcast) or per rank-block
   // Rank-blocks inside the in/out buffers start at multiples of these byte strides
   // (reduce-scatter, gather, scatter, allgather, alltoall).

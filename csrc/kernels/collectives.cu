@@ -60,6 +60,55 @@ __device__ __forceinline__ void copyOut(const CollArgs &a, int rank, int b, int 
 }
 
 // ---------------------------------------------------------------------------
+// run-time pointer exchange (buffers outside symmetric windows)
+// ---------------------------------------------------------------------------
+// The argument block lives in shared memory so that the peers' pointers can be
+// filled in once they are known.
+__device__ __forceinline__ CollArgs &stageArgs(const CollArgs &src) {
+  static_assert(sizeof(CollArgs) % 8 == 0, "argument block is copied in 8-byte words");
+  __shared__ __align__(16) unsigned long long words[sizeof(CollArgs) / 8];
+  for (int i = threadIdx.x; i < (int)(sizeof(CollArgs) / 8); i += blockDim.x)
+    words[i] = ((const unsigned long long *)&src)[i];
+  __syncthreads();
+  return *(CollArgs *)words;
+}
+
+// Before the first barrier: thread p tells rank p where this rank's input and output
+// are in rank p's address space.  The same thread then raises the barrier flag at rank
+// p with release semantics, so the pad is visible to whoever sees the flag.  CTA b only
+// ever meets CTA b of a peer, hence one pad entry per (CTA, source rank); two parities
+// because a fast rank may publish for its next launch while a slow one still has to
+// read this launch's entry (it cannot be two launches ahead: that takes a barrier).
+__device__ __forceinline__ void publishPointers(const flagcxDevComm &c, const CollArgs &a, int b) {
+  const int t = threadIdx.x;
+  if (a.xchg && t < c.nRanks && t != c.rank) {
+    unsigned long long *pad =
+        a.ptrPad[t] + (((size_t)a.xchgParity * FLAGCX_COLL_BARRIER_SLOTS + b) * FLAGCX_MAX_RANKS + c.rank) * 2;
+    fcxdev::stRelaxedSys(pad, (unsigned long long)(uintptr_t)a.pubIn[t]);
+    fcxdev::stRelaxedSys(pad + 1, (unsigned long long)(uintptr_t)a.pubOut[t]);
+  }
+}
+// After the first barrier: take the peers' pointers out of the local pad.
+__device__ __forceinline__ void learnPointers(const flagcxDevComm &c, CollArgs &a, int b) {
+  if (!a.xchg) return;
+  const int t = threadIdx.x;
+  if (t < c.nRanks && t != c.rank) {
+    const unsigned long long *pad =
+        a.ptrPad[c.rank] + (((size_t)a.xchgParity * FLAGCX_COLL_BARRIER_SLOTS + b) * FLAGCX_MAX_RANKS + t) * 2;
+    if (a.xchg & kXchgIn) a.in[t] = (const char *)(uintptr_t)fcxdev::ldRelaxedSys(pad);
+    if (a.xchg & kXchgOut) a.out[t] = (char *)(uintptr_t)fcxdev::ldRelaxedSys(pad + 1);
+  }
+  __syncthreads();
+}
+// The bulk-copy engine needs 16-byte aligned addresses; pointers learnt at run time
+// (or filled in by the emulated world's launcher) were not seen by the host's check.
+__device__ __forceinline__ bool learntPointersAligned(const flagcxDevComm &c, const CollArgs &a) {
+  uintptr_t bits = 0;
+  for (int p = 0; p < c.nRanks; ++p) bits |= (uintptr_t)a.in[p] | (uintptr_t)a.out[p];
+  return (bits & 15) == 0;
+}
+
+// ---------------------------------------------------------------------------
 // shared-memory ring of the bulk-copy paths (dynamic shared memory of the launch)
 // ---------------------------------------------------------------------------
 constexpr int kBulkMaxStages = 12;
@@ -335,14 +384,64 @@ struct Reducer {
   }
 };
 
+// Second phase of the casting two-shot all-reduce: `elems` 16-bit values of a reduced
+// slice (local or a peer's scratch) become fp32 in the local output, plus an optional
+// fp32 residual.  The CTA takes the share of the slice that the same CTA of the
+// slice's owner produced (same partition as Reducer::slice).
+template <typename T>
+__device__ void widenSlice(const T *src, float *dst, size_t elems, const float *residual, int b, int g) {
+  constexpr int N = 8;
+  size_t ub, ue;
+  ctaShare((elems * sizeof(T) + 15) >> 4, b, g, &ub, &ue);
+  const size_t eb = ub * N, ee = ue * N < elems ? ue * N : elems;
+  if (eb >= ee) return;
+  const bool vec = ((((uintptr_t)src) | ((uintptr_t)dst) | ((uintptr_t)residual)) & 15) == 0;
+  size_t done = eb;
+  if (vec) {
+    const size_t fullEnd = ee / N * N, stride = (size_t)blockDim.x * N;
+    auto emit = [&](size_t e, uint4 v) {
+      const T *h = (const T *)&v;
+      float f[N];
+#pragma unroll
+      for (int i = 0; i < N; ++i) f[i] = toAcc<T>(h[i]);
+      if (residual) {
+        uint4 r0 = ldLocal16(residual + e), r1 = ldLocal16(residual + e + 4);
+        const float *ra = (const float *)&r0, *rb = (const float *)&r1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[i] += ra[i]; f[4 + i] += rb[i]; }
+      }
+      st16(dst + e, *(uint4 *)&f[0]);
+      st16(dst + e + 4, *(uint4 *)&f[4]);
+    };
+    size_t e = eb + (size_t)threadIdx.x * N;
+    for (; e + 3 * stride < fullEnd; e += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ldSys16(src + e + u * stride);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) emit(e + u * stride, v[u]);
+    }
+    for (; e < fullEnd; e += stride) emit(e, ldSys16(src + e));
+    done = fullEnd > eb ? fullEnd : eb;
+  }
+  for (size_t e = done + threadIdx.x; e < ee; e += blockDim.x) {
+    float x = toAcc<T>(ldSysElem(src + e));
+    if (residual) x += residual[e];
+    dst[e] = x;
+  }
+}
+
 template <typename T, int OP, int NR>
-__device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
+__device__ void reduceBody(const flagcxDevComm &c, CollArgs &a) {
   const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
   using R = Reducer<T, OP, NR>;
 
   copyIn(a, rank, b, g);
+  publishPointers(c, a, b);
   if (a.flags & kFlagBeginBarrier)
     if (!ctaBarrier(c, b)) return;
+  learnPointers(c, a, b);
+  const bool bulk = NR > 0 && a.bulkStage && learntPointersAligned(c, a);
 
   char *local[1] = {a.out[rank]};
   switch (a.kind) {
@@ -353,7 +452,7 @@ __device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
       size_t s = sliceElems(a.count, n, sizeof(T));
       size_t sb = s * rank < a.count ? s * rank : a.count;
       size_t se = sb + s < a.count ? sb + s : a.count;
-      if (NR > 0 && a.bulkStage) {
+      if (bulk) {
         if (!R::sliceBulk(c, a, sb, se, a.out, n, sb, b, g)) return;
       } else {
         R::slice(a, n, sb, se, a.out, n, sb, b, g);
@@ -362,7 +461,7 @@ __device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
     }
     case kReduceScatter: {
       size_t sb = a.inStride / sizeof(T) * rank;
-      if (NR > 0 && a.bulkStage) {
+      if (bulk) {
         if (!R::sliceBulk(c, a, sb, sb + a.count, local, 1, 0, b, g)) return;
       } else {
         R::slice(a, n, sb, sb + a.count, local, 1, 0, b, g);
@@ -372,6 +471,37 @@ __device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
     case kReduceToRoot:
       if (rank == a.root) R::slice(a, n, 0, a.count, local, 1, 0, b, g);
       break;
+    case kAllReduceTwoShotCast: {
+      // 16-bit inputs, fp32 result.  Sending fp32 to every peer would double the NVLink
+      // bytes, so each rank rounds its reduced (and scaled) slice once to the input type
+      // into its own scratch, and every rank then pulls all slices and widens them while
+      // writing its output: the same bytes cross NVLink as in the plain all-reduce, and
+      // all ranks end up with identical values.
+      if constexpr (sizeof(T) == 2) {
+        const size_t s = sliceElems(a.count, n, sizeof(T));
+        const size_t sb = s * rank < a.count ? s * rank : a.count;
+        const size_t se = sb + s < a.count ? sb + s : a.count;
+        const char *residual = a.residual;
+        __syncthreads();
+        if (threadIdx.x == 0) { a.outMode = kOutSame; a.residual = nullptr; }
+        __syncthreads();
+        char *scratch[1] = {a.aux[rank]};
+        if (bulk) {
+          if (!R::sliceBulk(c, a, sb, se, scratch, 1, 0, b, g)) return;
+        } else {
+          R::slice(a, n, sb, se, scratch, 1, 0, b, g);
+        }
+        if (!ctaBarrier(c, b)) return;
+        for (int k = 0; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          const size_t pb = s * p < a.count ? s * p : a.count;
+          const size_t pe = pb + s < a.count ? pb + s : a.count;
+          widenSlice<T>((const T *)a.aux[p], (float *)a.out[rank] + pb, pe - pb,
+                        residual ? (const float *)residual + pb : nullptr, b, g);
+        }
+      }
+      break;
+    }
     default: break;
   }
 
@@ -380,17 +510,136 @@ __device__ void reduceBody(const flagcxDevComm &c, const CollArgs &a) {
   copyOut(a, rank, b, g);
 }
 
+// ---------------------------------------------------------------------------
+// LL family: small messages without any barrier
+// ---------------------------------------------------------------------------
+// Every 8 bytes of data travel in one 16-byte store {data0, flag, data1, flag} into a
+// slot that the receiver owns per sender; the receiver spins (bounded) until both
+// flags carry this operation's value, so data and "it has arrived" are one message.
+// Slots alternate between two parities: a rank can be at most one operation ahead of
+// a peer (it needs the peer's data to finish the current one), so the slot of operation
+// k is free again when operation k+2 writes it.  Only kinds in which every rank
+// receives from every rank may use this (all-reduce, all-gather).
+__device__ __forceinline__ void llLoadUnit(const char *src, size_t bytes, size_t u, uint32_t &d0, uint32_t &d1) {
+  const size_t off = u << 3;
+  if (off + 8 <= bytes && (((uintptr_t)src) & 7) == 0) {
+    uint2 v = *(const uint2 *)(src + off);
+    d0 = v.x;
+    d1 = v.y;
+    return;
+  }
+  unsigned char t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int i = 0; i < 8; ++i)
+    if (off + i < bytes) t[i] = (unsigned char)src[off + i];
+  d0 = (uint32_t)t[0] | ((uint32_t)t[1] << 8) | ((uint32_t)t[2] << 16) | ((uint32_t)t[3] << 24);
+  d1 = (uint32_t)t[4] | ((uint32_t)t[5] << 8) | ((uint32_t)t[6] << 16) | ((uint32_t)t[7] << 24);
+}
+__device__ __forceinline__ void llStoreUnit(char *dst, size_t bytes, size_t u, uint32_t d0, uint32_t d1) {
+  const size_t off = u << 3;
+  if (off + 8 <= bytes && (((uintptr_t)dst) & 7) == 0) {
+    *(uint2 *)(dst + off) = make_uint2(d0, d1);
+    return;
+  }
+  for (int i = 0; i < 8; ++i)
+    if (off + i < bytes) dst[off + i] = (char)(((i < 4 ? d0 : d1) >> (8 * (i & 3))) & 0xffu);
+}
+__device__ __forceinline__ void llSend(char *slot, uint32_t d0, uint32_t d1, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(slot), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
+               : "memory");
+}
+__device__ __forceinline__ bool llRecv(const flagcxDevComm &c, const char *slot, uint32_t flag, uint32_t &d0,
+                                       uint32_t &d1, unsigned peer) {
+  unsigned long long t0 = 0;
+  for (unsigned spins = 0;; ++spins) {
+    uint32_t f0, f1;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1)
+                 : "l"(slot)
+                 : "memory");
+    if (f0 == flag && f1 == flag) return true;
+    if ((spins & 1023u) == 1023u) {
+      if (c.status && fcxdev::ldVolatileU32(&c.status->abortFlag)) {
+        fcxdev::reportError(c.status, FLAGCX_DEV_ABORTED, FLAGCX_DEV_AT_KERNEL, peer, flag);
+        return false;
+      }
+      if (t0 == 0) t0 = fcxdev::globalTimerNs();
+      else if (fcxdev::globalTimerNs() - t0 > c.timeoutNs) {
+        fcxdev::reportError(c.status, FLAGCX_DEV_TIMEOUT, FLAGCX_DEV_AT_KERNEL, peer, flag);
+        return false;
+      }
+    }
+  }
+}
+
+template <typename T>
+__device__ void llBody(const flagcxDevComm &c, const CollArgs &a) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int N = 8 / (int)sizeof(T);
+  const int rank = c.rank, n = c.nRanks;
+  const size_t bytes = a.count * sizeof(T); // all-reduce: the message; all-gather: one rank's block
+  const size_t units = (bytes + 7) >> 3;
+  const size_t parityOff = (size_t)(a.llEpoch & 1u) * FLAGCX_MAX_RANKS * a.llSlotBytes;
+  const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nt = (size_t)gridDim.x * blockDim.x;
+  const char *in = a.in[rank];
+  for (size_t u = t; u < units; u += nt) {
+    uint32_t d0, d1;
+    llLoadUnit(in, bytes, u, d0, d1);
+    for (int k = 1; k < n; ++k) {
+      int p = rank + k; if (p >= n) p -= n;
+      llSend(a.aux[p] + parityOff + (size_t)rank * a.llSlotBytes + (u << 4), d0, d1, a.llEpoch);
+    }
+  }
+  const char *mine = a.aux[rank] + parityOff;
+  for (size_t u = t; u < units; u += nt) {
+    if (a.kind == kLlAllReduce) {
+      Acc acc[N];
+      for (int p = 0; p < n; ++p) { // rank order: every rank computes bit-identical results
+        uint32_t w[2];
+        if (p == rank) llLoadUnit(in, bytes, u, w[0], w[1]);
+        else if (!llRecv(c, mine + (size_t)p * a.llSlotBytes + (u << 4), a.llEpoch, w[0], w[1], (unsigned)p)) return;
+        const T *e = (const T *)w;
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = p == 0 ? toAcc<T>(e[i]) : combine<kOpRuntime, Acc>(acc[i], toAcc<T>(e[i]), a.redOp);
+      }
+      uint32_t o[2];
+      T *oe = (T *)o;
+#pragma unroll
+      for (int i = 0; i < N; ++i) oe[i] = fromAcc<T>(finish<Acc>(acc[i], a.scale, a.divisor));
+      llStoreUnit(a.out[rank], bytes, u, o[0], o[1]);
+    } else {
+      for (int k = 0; k < n; ++k) {
+        int p = rank + k; if (p >= n) p -= n;
+        uint32_t d0, d1;
+        if (p == rank) llLoadUnit(in, bytes, u, d0, d1);
+        else if (!llRecv(c, mine + (size_t)p * a.llSlotBytes + (u << 4), a.llEpoch, d0, d1, (unsigned)p)) return;
+        llStoreUnit(a.out[rank] + a.outStride * p, bytes, u, d0, d1);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    llKernel(const __grid_constant__ flagcxDevComm c, const __grid_constant__ CollArgs a) {
+  llBody<T>(c, a);
+}
+template <typename T>
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    llKernelEmu(const flagcxDevComm *cs, const CollArgs *as) {
+  llBody<T>(cs[blockIdx.y], as[blockIdx.y]);
+}
+
 template <typename T, int OP, int NR>
 __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
-    reduceKernel(const flagcxDevComm c, const CollArgs a) {
-  reduceBody<T, OP, NR>(c, a);
+    reduceKernel(const __grid_constant__ flagcxDevComm c, const __grid_constant__ CollArgs a) {
+  reduceBody<T, OP, NR>(c, stageArgs(a));
 }
 
 // Emulated world: one cooperative launch, blockIdx.y plays the rank.
 template <typename T, int OP, int NR>
 __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
     reduceKernelEmu(const flagcxDevComm *cs, const CollArgs *as) {
-  reduceBody<T, OP, NR>(cs[blockIdx.y], as[blockIdx.y]);
+  reduceBody<T, OP, NR>(cs[blockIdx.y], stageArgs(as[blockIdx.y]));
 }
 
 // ---------------------------------------------------------------------------
@@ -535,7 +784,7 @@ __device__ void ctaCopyShare(char *dst, const char *src, size_t bytes, int b, in
   ctaCopy(dst, src, bb, be);
 }
 
-__device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
+__device__ void copyBody(const flagcxDevComm &c, CollArgs &a) {
   const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
   const size_t es = a.elemSize;
   const size_t blk = a.count * es;
@@ -550,8 +799,11 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
     }
   }
   copyIn(a, rank, b, g);
+  publishPointers(c, a, b);
   if (a.flags & kFlagBeginBarrier)
     if (!ctaBarrier(c, b)) return;
+  learnPointers(c, a, b);
+  const bool bulk = a.bulkStage && learntPointersAligned(c, a);
 
   switch (a.kind) {
     case kAllGatherPush: {
@@ -563,7 +815,7 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
         if (p == rank && d == a.in[rank]) continue; // in place
         dst[nd++] = d;
       }
-      if (a.bulkStage) {
+      if (bulk) {
         const char *src0 = a.in[rank];
         if (!ctaBulkMove(c, &src0, dst, nd, true, blk, b, g, a.bulkStage, a.bulkDepth)) return;
       } else {
@@ -588,7 +840,7 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
           if (p == rank && a.in[rank] == a.out[rank]) continue;
           dst[nd++] = a.out[p];
         }
-        if (a.bulkStage) {
+        if (bulk) {
           const char *src0 = a.in[rank];
           if (!ctaBulkMove(c, &src0, dst, nd, true, blk, b, g, a.bulkStage, a.bulkDepth)) return;
         } else {
@@ -627,7 +879,7 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
         }
         vec &= ((((uintptr_t)src[k]) | ((uintptr_t)dst[k])) & 15) == 0;
       }
-      if (a.bulkStage && a.kind == kAllToAllPush) {
+      if (bulk && a.kind == kAllToAllPush) {
         if (!ctaBulkMove(c, src, dst, n, false, blk, b, g, a.bulkStage, a.bulkDepth)) return;
         break;
       }
@@ -682,12 +934,13 @@ __device__ void copyBody(const flagcxDevComm &c, const CollArgs &a) {
   copyOut(a, rank, b, g);
 }
 
-__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) copyKernel(const flagcxDevComm c, const CollArgs a) {
-  copyBody(c, a);
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    copyKernel(const __grid_constant__ flagcxDevComm c, const __grid_constant__ CollArgs a) {
+  copyBody(c, stageArgs(a));
 }
 __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
     copyKernelEmu(const flagcxDevComm *cs, const CollArgs *as) {
-  copyBody(cs[blockIdx.y], as[blockIdx.y]);
+  copyBody(cs[blockIdx.y], stageArgs(as[blockIdx.y]));
 }
 
 // ---------------------------------------------------------------------------
@@ -895,7 +1148,19 @@ cudaError_t launchReduceT(const LaunchCtx &lc, const CollArgs &a) {
   dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
   if (lc.emuRanks > 0) {
     void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
-    return cudaLaunchCooperativeKernel((const void *)reduceKernelEmu<T, OP, NR>, grid, block, params, 0, lc.stream);
+    size_t emuSmem = 0;
+    if (NR > 0 && lc.emuBulk) {
+      emuSmem = kBulkRingBytes;
+      static bool emuConfigured = false; // one per instantiation
+      if (!emuConfigured) {
+        cudaError_t e = cudaFuncSetAttribute(reduceKernelEmu<T, OP, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)emuSmem);
+        if (e != cudaSuccess) return e;
+        emuConfigured = true;
+      }
+    }
+    return cudaLaunchCooperativeKernel((const void *)reduceKernelEmu<T, OP, NR>, grid, block, params, emuSmem,
+                                       lc.stream);
   }
   size_t smem = 0;
   if (NR > 0 && a.bulkStage) {
@@ -944,11 +1209,51 @@ cudaError_t launchReduceKernel(const LaunchCtx &lc, const CollArgs &a, int nRank
   }
 }
 
+namespace {
+template <typename T>
+cudaError_t launchLlT(const LaunchCtx &lc, const CollArgs &a) {
+  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  if (lc.emuRanks > 0) {
+    void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
+    return cudaLaunchCooperativeKernel((const void *)llKernelEmu<T>, grid, block, params, 0, lc.stream);
+  }
+  llKernel<T><<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  return cudaGetLastError();
+}
+} // namespace
+
+cudaError_t launchLlKernel(const LaunchCtx &lc, const CollArgs &a) {
+  if (a.kind == kLlAllGather) return launchLlT<unsigned char>(lc, a); // bytes
+  switch ((flagcxDataType_t)a.dtype) {
+    case flagcxFloat32: return launchLlT<float>(lc, a);
+    case flagcxBfloat16: return launchLlT<__nv_bfloat16>(lc, a);
+    case flagcxFloat16: return launchLlT<__half>(lc, a);
+    case flagcxFloat64: return launchLlT<double>(lc, a);
+    case flagcxInt8: return launchLlT<signed char>(lc, a);
+    case flagcxUint8: return launchLlT<unsigned char>(lc, a);
+    case flagcxInt32: return launchLlT<int>(lc, a);
+    case flagcxUint32: return launchLlT<unsigned int>(lc, a);
+    case flagcxInt64: return launchLlT<long long>(lc, a);
+    case flagcxUint64: return launchLlT<unsigned long long>(lc, a);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
 cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a) {
   dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
   if (lc.emuRanks > 0) {
     void *params[] = {(void *)&lc.emuComms, (void *)&lc.emuArgs};
-    return cudaLaunchCooperativeKernel((const void *)copyKernelEmu, grid, block, params, 0, lc.stream);
+    size_t emuSmem = 0;
+    if (lc.emuBulk) {
+      emuSmem = kBulkRingBytes;
+      static bool emuConfigured = false;
+      if (!emuConfigured) {
+        cudaError_t e = cudaFuncSetAttribute(copyKernelEmu, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)emuSmem);
+        if (e != cudaSuccess) return e;
+        emuConfigured = true;
+      }
+    }
+    return cudaLaunchCooperativeKernel((const void *)copyKernelEmu, grid, block, params, emuSmem, lc.stream);
   }
   size_t smem = 0;
   if (a.bulkStage) {

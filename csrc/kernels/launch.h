@@ -18,6 +18,7 @@ struct LaunchCtx {
   const CollArgs *emuArgs = nullptr;
   const P2pArgs *emuP2p = nullptr;
   const void *emuBlob = nullptr; // per-rank argument blocks of the other kernel families
+  bool emuBulk = false;          // some emulated rank takes a bulk-copy path: the launch needs the shared-memory ring
 };
 
 struct MoeArgs;
@@ -30,6 +31,7 @@ cudaError_t launchReduceKernel(const LaunchCtx &lc, const CollArgs &a, int nRank
 cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a);
 cudaError_t launchP2pKernel(const LaunchCtx &lc, const P2pArgs &a);
 cudaError_t launchNvlsKernel(const LaunchCtx &lc, const CollArgs &a);
+cudaError_t launchLlKernel(const LaunchCtx &lc, const CollArgs &a);
 // One-sided host API (onesided.cu).  `arrival` is a zero-initialised device word the
 // CTAs of one put count themselves in; puts on one stream may share it.
 cudaError_t launchPutSignal(cudaStream_t s, void *dst, const void *src, size_t bytes, unsigned long long *peerSignal,

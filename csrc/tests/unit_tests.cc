@@ -14,6 +14,7 @@
 #include "../host/bootstrap.h"
 #include "../host/comm.h"
 #include "../host/cpu_coll.h"
+#include "../host/reg_cache.h"
 #include "../host/shm.h"
 #include "../host/tuner.h"
 #include "flagcx_net.h"
@@ -283,7 +284,90 @@ static void testShmRing() {
   EXPECT(processIsDead(getpid()) == false && processIsDead(0x3ffffff) == true);
 }
 
+// On-demand registration among three "ranks" (threads) with a backend that stands in
+// for the CUDA layer: allocations are heap blocks, "opening" a handle returns the
+// owner's address plus a per-opener offset so that each rank sees its own mapping.
+static void testRegCache() {
+  struct FakeAlloc { char *base; size_t size; uint64_t id; };
+  static std::mutex mu;
+  static std::vector<FakeAlloc> allocs;
+  static std::atomic<uint64_t> nextId{100};
+  static std::atomic<int> opens{0}, closes{0};
+  auto backendFor = [](int rank) {
+    RegBackend b;
+    b.identify = [](const void *p, void **base, size_t *size, uint64_t *id) {
+      std::lock_guard<std::mutex> g(mu);
+      for (auto &a : allocs)
+        if ((const char *)p >= a.base && (const char *)p < a.base + a.size) { *base = a.base; *size = a.size; *id = a.id; return true; }
+      return false;
+    };
+    b.exportHandle = [](void *base, void *handle) {
+      std::lock_guard<std::mutex> g(mu);
+      for (auto &a : allocs)
+        if (a.base == base) {
+          if (a.size == 4096) return false; // this size plays the allocation that cannot be exported
+          memset(handle, 0, kIpcHandleBytes);
+          memcpy(handle, &a.base, sizeof a.base);
+          memcpy((char *)handle + 8, &a.id, sizeof a.id);
+          return true;
+        }
+      return false;
+    };
+    b.open = [rank](const void *handle) -> void * {
+      char *base;
+      memcpy(&base, handle, sizeof base);
+      ++opens;
+      return base + ((size_t)(rank + 1) << 40); // a different address in every "process"
+    };
+    b.close = [](void *) { ++closes; };
+    return b;
+  };
+  auto alloc = [](size_t size) {
+    char *p = (char *)malloc(size);
+    std::lock_guard<std::mutex> g(mu);
+    allocs.push_back({p, size, nextId++});
+    return p;
+  };
+  const int n = 3;
+  const uint64_t key = 0xabcdef12345ull ^ (uint64_t)getpid();
+  RegCache rc[n];
+  for (int r = 0; r < n; ++r) EXPECT(rc[r].start(key, r, n, backendFor(r)) == flagcxSuccess);
+  char *x = alloc(1 << 16), *bad = alloc(4096);
+  void *va[FLAGCX_MAX_RANKS] = {};
+  // rank 1 exports x: ranks 0 and 2 open it, each at its own address; offsets carry over
+  EXPECT(rc[1].lookup(x + 256, 1024, va));
+  EXPECT(va[1] == x + 256 && va[0] == x + 256 + ((size_t)1 << 40) && va[2] == x + 256 + ((size_t)3 << 40));
+  EXPECT(opens.load() == 2);
+  EXPECT(rc[1].lookup(x, 1 << 16, va) && opens.load() == 2 && rc[1].counters().hits == 1);
+  EXPECT(!rc[1].lookup(x + 100, 1 << 16, va)); // runs past the allocation
+  // an allocation that cannot be exported: refused, and the verdict is remembered
+  EXPECT(!rc[0].lookup(bad, 16, va) && !rc[0].lookup(bad, 16, va) && rc[0].counters().refused == 1);
+  EXPECT(!rc[0].lookup(&key, 8, va)); // not a device allocation at all
+  // the address is freed and handed out again under a new id: peers unmap and map anew
+  {
+    std::lock_guard<std::mutex> g(mu);
+    for (auto &a : allocs) if (a.base == x) a.id = nextId++;
+  }
+  EXPECT(rc[1].lookup(x, 64, va) && rc[1].counters().stale == 1 && opens.load() == 4 && closes.load() == 2);
+  // two ranks register at the same time, each serving the other
+  std::thread t0([&] { void *v[FLAGCX_MAX_RANKS]; for (int i = 0; i < 50; ++i) { char *p = alloc(8192); EXPECT(rc[0].lookup(p, 8192, v)); } });
+  std::thread t2([&] { void *v[FLAGCX_MAX_RANKS]; for (int i = 0; i < 50; ++i) { char *p = alloc(8192); EXPECT(rc[2].lookup(p, 8192, v)); } });
+  t0.join();
+  t2.join();
+  EXPECT(rc[0].counters().exports == 50 && rc[2].counters().exports == 50);
+  rc[1].forget(x + 5);
+  EXPECT(closes.load() == 4);
+  const int openedBefore = opens.load();
+  for (int r = 0; r < n; ++r) rc[r].stop();
+  EXPECT(closes.load() == openedBefore); // everything a rank opened for its peers is unmapped at stop
+  EXPECT(!rc[1].lookup(x, 8, va));       // stopped: nothing is exportable any more
+  std::lock_guard<std::mutex> g(mu);
+  for (auto &a : allocs) free(a.base);
+  allocs.clear();
+}
+
 int main() {
+  testRegCache();
   testShmRing();
   testParams();
   testIfMatcher();

@@ -68,6 +68,12 @@ class OpStats(C.Structure):
                 ("lastCtas", C.c_int), ("lastMs", C.c_float)]
 
 
+class UserBufferStats(C.Structure):
+    """Counters of the on-demand export of user buffers (flagcxCommUserBufferStats)."""
+    _fields_ = [("enabled", C.c_int), ("hits", C.c_uint64), ("exports", C.c_uint64), ("refused", C.c_uint64),
+                ("stale", C.c_uint64), ("peerOpened", C.c_uint64), ("peerClosed", C.c_uint64)]
+
+
 class WaitSignalDesc(C.Structure):
     _fields_ = [("opCnt", C.c_uint64), ("peer", C.c_int)]
 
@@ -241,6 +247,11 @@ class Comm:
     def stats(self, op: int) -> OpStats:
         s = OpStats()
         check(lib().flagcxCommGetStats(self.h, op, C.byref(s)), "flagcxCommGetStats", self.h)
+        return s
+
+    def user_buffer_stats(self) -> UserBufferStats:
+        s = UserBufferStats()
+        check(lib().flagcxCommUserBufferStats(self.h, C.byref(s)), "flagcxCommUserBufferStats", self.h)
         return s
 
     # -- collectives (buffers: numpy arrays, torch tensors or raw addresses) ---------

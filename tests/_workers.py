@@ -328,6 +328,63 @@ def gpu_collectives(rank, n, uid, count, registered):
     return worst
 
 
+def gpu_user_buffers_under_skew(rank, n, uid, rounds):
+    """Ordinary torch tensors (nothing registered by the caller), ranks with different
+    allocation histories, one rank held back by compute before every collective: a small
+    all-reduce directly followed by a large all-reduce / reduce-scatter / all-gather,
+    exact results every round.  Runs with on-demand export of user buffers (the default)
+    and, with FLAGCX_USER_BUFFER_EXPORT=0, through the staging window."""
+    import torch
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    assert comm.device_path, "expected the NVLink device path"
+    exporting = bool(comm.user_buffer_stats().enabled)
+    # different allocation histories: segments and offsets differ between the ranks
+    ballast = [torch.empty((rank + 1) * (3 << 20) + 4096 * i, dtype=torch.uint8, device="cuda") for i in range(rank + 2)]
+    small_n, big_n, per = 1024, (6 << 20) + 16 * n, (1 << 20)
+    busy = torch.randn(2048, 2048, device="cuda")
+    bad = []
+    for it in range(rounds):
+        # integers small enough that every sum is exact in fp32
+        small = torch.full((small_n,), float(rank + it), device="cuda")
+        big = (torch.arange(big_n, device="cuda", dtype=torch.float32) % 1000) + rank
+        rs_in = (torch.arange(per * n, device="cuda", dtype=torch.float32) % 512) * (rank + 1)
+        rs_out = torch.empty(per, device="cuda")
+        ag_out = torch.empty(per * n, device="cuda")
+        if it % n == rank:  # this round's straggler
+            for _ in range(20):
+                busy = (busy @ busy).clamp_(-1, 1)
+        comm.all_reduce(small, small, small_n, capi.FLOAT, capi.SUM)
+        comm.all_reduce(big, big, big_n, capi.FLOAT, capi.SUM)
+        comm.all_reduce(small, small, small_n, capi.FLOAT, capi.SUM)
+        comm.reduce_scatter(rs_in, rs_out, per, capi.FLOAT, capi.SUM)
+        comm.all_gather(rs_out, ag_out, per, capi.FLOAT)
+        torch.cuda.synchronize()
+        base = sum(range(n))
+        want_small = float((n * it + base) * n)
+        if not bool((small == want_small).all()):
+            bad.append(("small", it))
+        want_big = (torch.arange(big_n, device="cuda", dtype=torch.float32) % 1000) * n + base
+        if not torch.equal(big, want_big):
+            bad.append(("big", it))
+        tri = n * (n + 1) // 2
+        want_rs = (torch.arange(per * n, device="cuda", dtype=torch.float32) % 512) * tri
+        if not torch.equal(rs_out, want_rs[rank * per:(rank + 1) * per]):
+            bad.append(("reduce_scatter", it))
+        if not torch.equal(ag_out, want_rs):
+            bad.append(("all_gather", it))
+        if it % 3 == 2:  # hand the segments back so that addresses get reused by new allocations
+            del small, big, rs_in, rs_out, ag_out, want_big, want_rs
+            torch.cuda.empty_cache()
+    st = comm.user_buffer_stats()
+    assert comm.async_error() == 0, comm.last_error()
+    comm.barrier()
+    del ballast
+    comm.destroy()
+    return {"bad": bad, "exporting": exporting, "exports": int(st.exports), "hits": int(st.hits),
+            "refused": int(st.refused), "stale": int(st.stale)}
+
+
 def gpu_peer_never_launches(rank, n, uid):
     """One rank skips the collective: the others' kernels give up after the time limit
     and report a remote error; nobody hangs and no GPU faults."""

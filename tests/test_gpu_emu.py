@@ -313,6 +313,159 @@ def test_staged_paths_for_unregistered_buffers():
         del os.environ["FLAGCX_EMU_FORCE_STAGING"]
 
 
+def _all_collectives_once(n, count, dt, shift):
+    """Every collective on fresh buffers that start `shift` elements into their allocation."""
+    comms = world(n)
+    tdt = TORCH_DT[dt]
+
+    def buf(numel, fill=None):
+        t = torch.zeros(numel + shift, dtype=tdt, device="cuda")[shift:]
+        if fill is not None:
+            t.copy_(fill)
+        return t
+
+    xs = [buf(count * n, x) for x in make_inputs(n, count * n, dt)]
+    ref = reference(xs, capi.SUM)
+    # all-reduce: one-shot out of place, two-shot out of place and in place
+    for algo, inplace in ((capi.ALGO_ONESHOT, False), (capi.ALGO_TWOSHOT, False), (capi.ALGO_TWOSHOT, True)):
+        ins = [buf(count * n, x) for x in xs]
+        outs = ins if inplace else [buf(count * n) for _ in range(n)]
+        for r in range(n):
+            comms[r].all_reduce_fused(ins[r], outs[r], count * n, dt, capi.SUM, algo=algo)
+        torch.cuda.synchronize()
+        assert_no_device_error(comms)
+        for r in range(n):
+            check_close(outs[r], ref, dt, n, f"allreduce algo {algo} inplace {inplace} rank {r}")
+    rs = [buf(count) for _ in range(n)]
+    for r in range(n):
+        comms[r].reduce_scatter(xs[r], rs[r], count, dt, capi.SUM)
+    torch.cuda.synchronize()
+    for r in range(n):
+        check_close(rs[r], ref[r * count:(r + 1) * count], dt, n, f"reduce-scatter rank {r}")
+    for algo in (capi.ALGO_PUSH, capi.ALGO_PULL):
+        ag = [buf(count * n) for _ in range(n)]
+        for r in range(n):
+            comms[r].all_gather(rs[r], ag[r], count, dt, algo=algo)
+        torch.cuda.synchronize()
+        for r in range(n):
+            assert torch.equal(ag[r], torch.cat(rs)), f"allgather algo {algo} rank {r}"
+    # all-gather in place: the input is the rank's own block of the output
+    ag = [buf(count * n) for _ in range(n)]
+    for r in range(n):
+        ag[r][r * count:(r + 1) * count].copy_(rs[r])
+        comms[r].all_gather(ag[r][r * count:(r + 1) * count], ag[r], count, dt)
+    torch.cuda.synchronize()
+    for r in range(n):
+        assert torch.equal(ag[r], torch.cat(rs)), f"in-place allgather rank {r}"
+    aa = [buf(count * n) for _ in range(n)]
+    for r in range(n):
+        comms[r].all_to_all(xs[r], aa[r], count, dt)
+    root = n - 1
+    bc = [buf(count, xs[r][:count]) for r in range(n)]
+    for r in range(n):
+        comms[r].broadcast(bc[r], bc[r], count, dt, root)
+    rd = [buf(count) for _ in range(n)]
+    for r in range(n):
+        comms[r].reduce(xs[r], rd[r], count, dt, capi.SUM, root)
+    ga = [buf(count * n) for _ in range(n)]
+    for r in range(n):
+        comms[r].gather(xs[r], ga[r], count, dt, root)
+    sc = [buf(count) for _ in range(n)]
+    for r in range(n):
+        comms[r].scatter(xs[r], sc[r], count, dt, root)
+    torch.cuda.synchronize()
+    assert_no_device_error(comms)
+    for r in range(n):
+        assert torch.equal(aa[r], torch.cat([xs[p][r * count:(r + 1) * count] for p in range(n)])), "alltoall"
+        assert torch.equal(bc[r], xs[root][:count]), "broadcast"
+        assert torch.equal(sc[r], xs[root][r * count:(r + 1) * count]), "scatter"
+    check_close(rd[root], reference([x[:count] for x in xs], capi.SUM), dt, n, "reduce")
+    assert torch.equal(ga[root], torch.cat([x[:count] for x in xs])), "gather"
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("shift", [0, 1])
+def test_pointer_exchange_for_buffers_outside_windows(n, shift):
+    """Buffers that are not inside a symmetric window: every rank tells its peers inside
+    the kernel where its buffer is (the path ordinary torch tensors take between
+    processes).  shift=1 starts every buffer off a 16-byte boundary."""
+    os.environ["FLAGCX_EMU_EXCHANGE"] = "1"
+    try:
+        _all_collectives_once(n, 3001, capi.FLOAT, shift)
+        _all_collectives_once(n, 777, capi.BFLOAT16, shift)
+    finally:
+        del os.environ["FLAGCX_EMU_EXCHANGE"]
+
+
+def test_pointer_exchange_alltoallv():
+    os.environ["FLAGCX_EMU_EXCHANGE"] = "1"
+    try:
+        n = 4
+        comms = world(n)
+        counts = [[(r * 3 + p) % 5 * 64 + (1 if (r + p) % 2 else 0) for p in range(n)] for r in range(n)]
+        sends, recvs, sd, rd = [], [], [], []
+        for r in range(n):
+            sc, rc = counts[r], [counts[p][r] for p in range(n)]
+            sd.append([sum(sc[:i]) for i in range(n)])
+            rd.append([sum(rc[:i]) for i in range(n)])
+            sends.append((torch.arange(sum(sc), dtype=torch.float32) + 10000 * r).cuda())
+            recvs.append(torch.zeros(sum(rc), device="cuda"))
+        for _ in range(3):  # consecutive launches alternate the pad parity
+            for r in range(n):
+                comms[r].all_to_allv(sends[r], counts[r], sd[r], recvs[r], [counts[p][r] for p in range(n)], rd[r],
+                                     capi.FLOAT)
+        torch.cuda.synchronize()
+        assert_no_device_error(comms)
+        for r in range(n):
+            for p in range(n):
+                want = sends[p][sd[p][r]:sd[p][r] + counts[p][r]]
+                assert torch.equal(recvs[r][rd[r][p]:rd[r][p] + counts[p][r]], want)
+    finally:
+        del os.environ["FLAGCX_EMU_EXCHANGE"]
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("exchange", [False, True])
+def test_bulk_copy_engine_paths(n, exchange):
+    """The large-message paths (one thread per CTA driving bulk copies through a ring of
+    shared-memory stages; reduce inputs fetched by bulk loads), forced at small sizes."""
+    env = {"FLAGCX_BULK_COPY_MIN_BYTES": "65536", "FLAGCX_BULK_ALLREDUCE_MIN_BYTES": "65536"}
+    if exchange:
+        env["FLAGCX_EMU_EXCHANGE"] = "1"
+    os.environ.update(env)
+    try:
+        comms = world(n)
+        for dt, count in ((capi.BFLOAT16, (1 << 19) + 8 * n), (capi.FLOAT, 3 * (1 << 17))):
+            xs = make_inputs(n, count * n, dt)
+            ref = reference(xs, capi.SUM)
+            outs = [torch.empty_like(x) for x in xs]
+            for r in range(n):
+                comms[r].all_reduce_fused(xs[r], outs[r], count * n, dt, capi.SUM, algo=capi.ALGO_TWOSHOT)
+            rs = [torch.empty(count, dtype=TORCH_DT[dt], device="cuda") for _ in range(n)]
+            for r in range(n):
+                comms[r].reduce_scatter(xs[r], rs[r], count, dt, capi.SUM)
+            ag = [torch.zeros(count * n, dtype=TORCH_DT[dt], device="cuda") for _ in range(n)]
+            for r in range(n):
+                comms[r].all_gather(rs[r], ag[r], count, dt, algo=capi.ALGO_PUSH)
+            aa = [torch.zeros(count * n, dtype=TORCH_DT[dt], device="cuda") for _ in range(n)]
+            for r in range(n):
+                comms[r].all_to_all(xs[r], aa[r], count, dt)
+            bc = [xs[r][:count * n].clone() for r in range(n)]
+            for r in range(n):
+                comms[r].broadcast(bc[r], bc[r], count * n, dt, 0)
+            torch.cuda.synchronize()
+            assert_no_device_error(comms)
+            for r in range(n):
+                check_close(outs[r], ref, dt, n, f"two-shot rank {r}")
+                check_close(rs[r], ref[r * count:(r + 1) * count], dt, n, f"reduce-scatter rank {r}")
+                assert torch.equal(ag[r], torch.cat(rs)), f"allgather rank {r}"
+                assert torch.equal(aa[r], torch.cat([xs[p][r * count:(r + 1) * count] for p in range(n)])), "alltoall"
+                assert torch.equal(bc[r], xs[0]), "broadcast"
+    finally:
+        for k in env:
+            del os.environ[k]
+
+
 def test_barrier_and_stats():
     n = 8
     comms = world(n)

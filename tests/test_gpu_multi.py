@@ -32,6 +32,22 @@ def test_device_collectives_on_real_peers(registered, count):
 
 
 @needs2
+@pytest.mark.parametrize("export", [True, False])
+def test_plain_tensors_with_a_straggler(export):
+    """No buffer is registered by the caller.  With export on, allocations are mapped into
+    the peers on first use (no staging copies); with it off, everything goes through the
+    staging window, small and large collectives back to back."""
+    n = 4 if ngpus() >= 4 else 2
+    env = {} if export else {"FLAGCX_USER_BUFFER_EXPORT": "0"}
+    res = run_ranks(n, "gpu_user_buffers_under_skew", 9, env=env, timeout=300)
+    for rank, out in res.items():
+        assert not out["bad"], (rank, out)
+        assert out["exporting"] == export
+        if export:
+            assert out["exports"] > 0 and out["hits"] > 0 and out["refused"] == 0, (rank, out)
+
+
+@needs2
 def test_missing_peer_becomes_an_error_code():
     n = 2
     env = {"NCCL_NVLS_ENABLE": "0", "FLAGCX_NVLS_ENABLE": "0"}
