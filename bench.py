@@ -174,10 +174,11 @@ def run_ours(args) -> dict:
         "dtype": "bf16",
         "data": "synthetic uniform-random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
-        "config": {"model": args.model, "params": cfg.num_params(), "global_batch": world, "seq_len": seq,
-                   "parallelism": f"fsdp{world}", "optimizer": "AdamW (bf16 states, fused kernel)",
-                   "l2": "no flush needed: each step streams 16 GB of parameters plus activations, far above the 126 MB L2",
-                   "backend": "flagcx (NVLink kernels of this repository)" if world > 1 else "single GPU, no collectives"},
+        "config": {"model": args.model, "global_batch": world, "seq_len": seq, "parallelism": f"fsdp{world}",
+                   "optimizer": "AdamW, fused kernel, bf16 states",
+                   "l2": "no flush needed: each step streams 16 GB of parameters plus activations, far above the 126 MB L2"},
+        "backend": "flagcx (NVLink kernels of this repository)" if world > 1 else "single GPU, no collectives",
+        "params": cfg.num_params(),
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": (seq + 1) * 8, "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
@@ -196,7 +197,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ours_pg", "nccl"],
+                    help="ours: this repository's sharding engine and kernels; reference: the unmodified FlagCX plugin under "
+                         "torch FSDP; ours_pg / nccl: the reference arm's exact model and FSDP code over this repository's "
+                         "ProcessGroup / over NCCL")
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=4096)
     args = ap.parse_args()
@@ -204,6 +208,9 @@ def main():
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
         out = run_reference(args)
+    elif args.impl in ("ours_pg", "nccl"):
+        from baseline.reference_arm import run_torch_fsdp
+        out = run_torch_fsdp(args, args.impl)
     else:
         out = run_ours(args)
     if out:

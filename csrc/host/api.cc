@@ -34,6 +34,9 @@ Route routeFor(flagcxComm *c, const void *a, const void *b) {
   return c->devicePath ? kRouteDevice : kRouteStaged;
 }
 
+} // namespace
+
+namespace fcx {
 flagcxResult_t ensureHostNet(flagcxComm *c) {
   if (c->hostNet) return flagcxSuccess;
   if (!c->bootstrap) return flagcxNotSupported;
@@ -42,6 +45,9 @@ flagcxResult_t ensureHostNet(flagcxComm *c) {
   c->cpu.net = c->hostNet.get();
   return flagcxSuccess;
 }
+} // namespace fcx
+
+namespace {
 
 flagcxResult_t hostStage(flagcxComm *c, size_t bytes, char **out) {
   if (c->hostStageBytes < bytes) {
@@ -381,6 +387,11 @@ static flagcxResult_t runCollective(flagcxComm *c, DeviceCollRequest &rq, size_t
     FCXCHECK(ensureHostNet(c));
     return host(rq.send, rq.recv);
   }
+  // ranks in several NVLink domains: two-level route for the operations that have one
+  if (c->intra && rq.op == flagcxCommOpAllReduce)
+    return hierAllReduce(c, rq.send, rq.recv, rq.count, rq.dtype, rq.redOp, rawStream(stream));
+  if (c->intra && rq.op == flagcxCommOpAllGather)
+    return hierAllGather(c, rq.send, rq.recv, rq.count, rq.dtype, rawStream(stream));
   // in-place device calls must see the input in the receive staging too
   return stagedCall(c, rq.send, sendBytes, rq.recv, recvBytes, rawStream(stream), [&](char *s, char *r) {
     return host(s, r);
@@ -848,6 +859,16 @@ flagcxResult_t flagcxCommUserBufferStats(flagcxComm_t comm, flagcxUserBufferStat
     out->peerOpened = k.opened;
     out->peerClosed = k.closed;
   }
+  return flagcxSuccess;
+}
+flagcxResult_t flagcxCommSetAutoExport(flagcxComm_t comm, int on) {
+  FCX_COMMCHECK(comm);
+  comm->autoExport = on != 0 && comm->exportUserBuffers;
+  return flagcxSuccess;
+}
+flagcxResult_t flagcxCommForgetUserBuffer(flagcxComm_t comm, const void *ptr) {
+  FCX_COMMCHECK(comm);
+  if (comm->reg && ptr) comm->reg->forget(ptr);
   return flagcxSuccess;
 }
 flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes) {

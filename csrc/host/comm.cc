@@ -30,6 +30,9 @@ FCX_PARAM(NvlsEnable, "NVLS_ENABLE", 0)
 FCX_PARAM(WatchdogMs, "WATCHDOG_MS", 200)
 FCX_PARAM(P2pSlotBytes, "P2P_SLOT_BYTES", 4ll << 20)
 FCX_PARAM(UserBufferExport, "USER_BUFFER_EXPORT", 1)
+// largest message (bytes of data) the LL slots can hold; every rank keeps
+// 2 * FLAGCX_MAX_RANKS slots of twice this size
+FCX_PARAM(LlSlotDataBytes, "LL_SLOT_BYTES", 64 << 10)
 
 // ---------------------------------------------------------------------------
 // window registry
@@ -92,6 +95,13 @@ SyncLayout makeLayout() {
   off += (size_t)FLAGCX_MAX_RANKS * FLAGCX_P2P_CTAS * sizeof(uint64_t);
   l.ptrPadOff = off;
   off += (size_t)FLAGCX_PTRPAD_WORDS * sizeof(uint64_t);
+  l.ringOff = off;
+  off += (size_t)FLAGCX_COLL_BARRIER_SLOTS * sizeof(uint64_t);
+  // LL slots are compared against flag values: they start zeroed like the pads above
+  off = alignUp(off, 256);
+  l.llOff = off;
+  l.llSlotBytes = alignUp((size_t)std::max<int64_t>(paramLlSlotDataBytes(), 1024) * 2, 256);
+  off += 2 * (size_t)FLAGCX_MAX_RANKS * l.llSlotBytes;
   off = alignUp(off, 1 << 16);
   l.zeroedBytes = off;
   l.stagingOff = off;
@@ -136,6 +146,7 @@ void fillDevComm(flagcxComm *c) {
   d.timeoutNs = (unsigned long long)std::max<int64_t>(readParam("WAIT_TIMEOUT_MS", paramWaitTimeoutMs()), 1) * 1000000ull;
   d.nSignals = FLAGCX_MAX_SIGNALS;
   d.nCounters = FLAGCX_MAX_COUNTERS;
+  d.nvlsBarrier = d.mcSignalPad && readParam("NVLS_BARRIER", 0) != 0 ? 1 : 0;
 }
 
 flagcxResult_t allocLocalDeviceState(flagcxComm *c) {
@@ -365,6 +376,7 @@ static flagcxResult_t setupDeviceWorld(flagcxComm *c, const std::vector<PeerInfo
       for (int v : up) all &= v != 0;
     }
     c->exportUserBuffers = all;
+    c->autoExport = all && readParam("USER_BUFFER_EXPORT", paramUserBufferExport()) >= 2;
     if (!all && c->reg) { c->reg->stop(); c->reg.reset(); }
   }
   FCX_INFO(SUB_INIT, "rank %d: device path over NVLink, %d ranks, staging %zu MiB, nvls %d, user-buffer export %d",
@@ -449,6 +461,17 @@ flagcxResult_t commCreate(flagcxComm **out, int nranks, const flagcxUniqueId &id
     c->watchdog = std::thread(watchdogMain, c.get());
   } else {
     FCX_INFO(SUB_INIT, "rank %d: host path (sockets)%s", rank, me.cudaDev >= 0 ? " with staged device buffers" : "");
+    // several NVLink domains: NVLink kernels inside each, the host network between them
+    bool gpus = true;
+    std::vector<uint64_t> hashes(nranks);
+    std::vector<int> hasGpu(nranks);
+    for (int p = 0; p < nranks; ++p) {
+      hashes[p] = peers[p].hostHash;
+      hasGpu[p] = peers[p].cudaDev >= 0;
+      gpus &= hasGpu[p] != 0;
+    }
+    if (gpus && nranks > 1 && readParam("P2P_DISABLE", paramP2pDisable()) == 0 && !getEnv("FLAGCX_FORCE_HOST"))
+      FCXCHECK(hierSetup(c.get(), hashes, hasGpu));
   }
   *out = c.release();
   return flagcxSuccess;
@@ -476,6 +499,7 @@ flagcxResult_t commDestroy(flagcxComm *c) {
   if (c->emu) return emuWorldDestroy(c);
   c->watchdogStop.store(true);
   if (c->watchdog.joinable()) c->watchdog.join();
+  hierTeardown(c);
   if (c->devicePath) {
     cudaSetDevice(c->cudaDev);
     cudaDeviceSynchronize();

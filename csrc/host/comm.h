@@ -88,6 +88,8 @@ struct SyncLayout {
   size_t inboxOff, signalOff, metaOff, p2pReadyOff, p2pDoneOff, ptrPadOff, zeroedBytes;
   size_t stagingOff, stagingBytes;   // collectives on unregistered buffers
   size_t p2pStageOff, p2pSlotBytes;  // send/recv: FLAGCX_MAX_RANKS slots
+  size_t llOff, llSlotBytes;         // LL slots: [parity 2][sender FLAGCX_MAX_RANKS][llSlotBytes]
+  size_t ringOff;                    // ring step flags: one u64 per CTA slot
   size_t total;
 };
 
@@ -120,7 +122,14 @@ struct flagcxComm {
   // exchange.  Off (legacy in-kernel staging) when any rank could not start the service.
   std::unique_ptr<fcx::RegCache> reg;
   bool exportUserBuffers = false;
-  uint64_t xchgSeq = 0;            // exchanging launches so far (same on every rank)
+  // Export any buffer a collective meets, not only those the caller registered with
+  // flagcxCommRegister.  Only safe when the library hears about frees (an exported
+  // allocation must be unmapped at the peers before it is freed): set by allocator
+  // integrations (the torch backend) or by FLAGCX_USER_BUFFER_EXPORT=2.
+  bool autoExport = false;
+  uint64_t xchgSeq = 0;            // collective launches so far (same on every rank)
+  uint64_t llSeq = 0;              // LL operations so far (same on every rank)
+  uint64_t ringSeq = 0;            // ring steps so far (same on every rank)
   void *bounce[2] = {nullptr, nullptr}; // exportable stand-ins for buffers that are not (input, output)
   size_t bounceBytes[2] = {0, 0};
   int winSeq = 0;                  // window registrations so far (same on every rank)
@@ -158,6 +167,12 @@ struct flagcxComm {
   // staged fallback when ranks cannot reach each other over NVLink
   void *hostStage = nullptr;
   size_t hostStageBytes = 0;
+  // two-level route (hier.cc): child communicator of this node's ranks, node geometry,
+  // pinned and device scratch of the inter-node step
+  flagcxComm *intra = nullptr;
+  int nNodes = 1, nodeRanks = 0;
+  void *hierPinned = nullptr, *hierDev = nullptr;
+  size_t hierPinnedBytes = 0, hierDevBytes = 0;
 };
 
 namespace fcx {
@@ -198,6 +213,14 @@ struct DeviceCollRequest {
 flagcxResult_t deviceCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream);
 flagcxResult_t deviceGroupLaunch(flagcxComm *c);
 flagcxResult_t deviceBarrier(flagcxComm *c, cudaStream_t stream);
+
+// hier.cc -- two-level route for communicators that span several NVLink domains
+flagcxResult_t hierSetup(flagcxComm *c, const std::vector<uint64_t> &hostHashes, const std::vector<int> &hasGpu);
+void hierTeardown(flagcxComm *c);
+flagcxResult_t hierAllReduce(flagcxComm *c, const void *send, void *recv, size_t count, flagcxDataType_t dt,
+                             flagcxRedOp_t op, cudaStream_t stream);
+flagcxResult_t hierAllGather(flagcxComm *c, const void *send, void *recv, size_t count, flagcxDataType_t dt,
+                             cudaStream_t stream);
 
 // emu.cc
 flagcxResult_t emuWorldCreate(int nranks, int dev, flagcxComm **comms);

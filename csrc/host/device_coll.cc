@@ -16,7 +16,7 @@ namespace fcx {
 
 namespace {
 
-enum Family { kFamReduce = 0, kFamCopy = 1, kFamNvls = 2 };
+enum Family { kFamReduce = 0, kFamCopy = 1, kFamNvls = 2, kFamP2p = 3, kFamLl = 4 };
 
 struct BufView {
   Window *win = nullptr;
@@ -117,6 +117,12 @@ flagcxResult_t resolve(flagcxComm *c, const void *p, size_t bytes, int which, cu
   u->view = viewOf(c, p, bytes);
   if (u->view.visible()) { u->reach = kReachWindow; return flagcxSuccess; }
   if (!c->exportUserBuffers || c->nranks == 1) return flagcxSuccess;
+  if (!c->autoExport) {
+    // only what the caller registered (flagcxCommRegister, on every rank) is exported;
+    // anything else goes through the staging window
+    if (c->reg->lookupKnown(p, bytes ? bytes : 1, u->peerVa)) u->reach = kReachExport;
+    return flagcxSuccess;
+  }
   if (c->reg->lookup(p, bytes ? bytes : 1, u->peerVa)) { u->reach = kReachExport; return flagcxSuccess; }
   void *b = nullptr;
   FCXCHECK(bounceBuffer(c, which, bytes, &b));
@@ -197,18 +203,21 @@ int bulkStageFor(flagcxComm *c, const CollArgs &a) {
 // The sum reductions at 2, 4 and 8 ranks have a variant whose inputs arrive through
 // the bulk-copy engine (Reducer::sliceBulk).  1 selects it.
 int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
-  if (a.kind != kAllReduceTwoShot && a.kind != kReduceScatter) return 0;
+  if (a.kind != kAllReduceTwoShot && a.kind != kAllReduceTwoShotCast && a.kind != kReduceScatter) return 0;
   const int n = c->nranks;
   if (a.redOp != kOpSum || (n != 2 && n != 4 && n != 8)) return 0;
   if (a.dtype != flagcxFloat32 && a.dtype != flagcxBfloat16 && a.dtype != flagcxFloat16) return 0;
   // measured on 8 B200s: reduce-scatter gains from 64 MB of peer input on (667 against 606 GB/s
   // at 4 GiB), the two-shot all-reduce only from about 400 MB on
-  const int64_t enable = readParam("BULK_REDUCE", 1), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20),
+  // Off by default: with the default cap of 32 CTAs the per-thread loads reach 555 GB/s on a
+  // B200 pair (436 MB reduce-scatter) where this path reaches 263; it only catches up near
+  // 96 CTAs, which a collective that runs beside GEMMs should not take.
+  const int64_t enable = readParam("BULK_REDUCE", 0), minBytes = readParam("BULK_COPY_MIN_BYTES", 64 << 20),
                 minAllReduce = readParam("BULK_ALLREDUCE_MIN_BYTES", 400 << 20);
   const size_t es = (size_t)a.elemSize, bytes = a.count * es;
   if (!enable || bytes % 16) return 0;
   const size_t slice = a.kind == kReduceScatter ? a.count : sliceElems(a.count, n, es);
-  if (slice * es * (size_t)(n - 1) < (size_t)(a.kind == kAllReduceTwoShot ? std::max(minBytes, minAllReduce) : minBytes)) return 0;
+  if (slice * es * (size_t)(n - 1) < (size_t)(a.kind != kReduceScatter ? std::max(minBytes, minAllReduce) : minBytes)) return 0;
   if (a.outMode == kOutBf16 && slice % 8) return 0; // output slices must start on 16 bytes too
   uintptr_t bits = (uintptr_t)a.residual | (a.kind == kReduceScatter ? a.inStride : 0);
   for (int p = 0; p < n; ++p) bits |= (uintptr_t)a.in[p] | (uintptr_t)a.out[p];
@@ -236,6 +245,7 @@ flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a0, int nCtas, 
   cudaError_t e;
   if (family == kFamCopy) e = launchCopyKernel(lc, a);
   else if (family == kFamReduce) e = launchReduceKernel(lc, a, c->nranks);
+  else if (family == kFamLl) e = launchLlKernel(lc, a);
   else e = launchNvlsKernel(lc, a);
   if (e != cudaSuccess) {
     FCX_WARN("kernel launch failed: %s", cudaGetErrorString(e));
@@ -300,6 +310,44 @@ int pickCtas(flagcxComm *c, const DeviceCollRequest &rq, const TuneChoice &ch) {
   return std::max(1, std::min(n, FLAGCX_COLL_BARRIER_SLOTS));
 }
 
+// ---- ring kinds ---------------------------------------------------------------------------
+// Step flags and, for the reducing kinds, the partial-sum scratch (the staging window cut
+// into n-1 slots).  Returns the largest slot in elements of `es` bytes.
+size_t setRing(flagcxComm *c, CollArgs &a, size_t es, int steps) {
+  const int n = c->nranks, next = (c->rank + 1) % n;
+  a.ringNext = (unsigned long long *)((char *)c->internalWin->peer[next] + c->layout.ringOff);
+  a.ringMine = (unsigned long long *)((char *)c->internalWin->peer[c->rank] + c->layout.ringOff);
+  a.ringBase = c->ringSeq;
+  c->ringSeq += (uint64_t)steps;
+  for (int p = 0; p < n; ++p) a.aux[p] = (char *)c->internalWin->peer[p] + c->layout.stagingOff;
+  const size_t slot = c->layout.stagingBytes / (size_t)std::max(1, n - 1) / es / 16 * 16;
+  a.ringSlotElems = slot;
+  return slot;
+}
+
+// ---- LL: small messages ---------------------------------------------------------------
+flagcxResult_t launchLl(flagcxComm *c, CollArgs &a, size_t bytes, cudaStream_t stream) {
+  for (int p = 0; p < c->nranks; ++p) a.aux[p] = (char *)c->internalWin->peer[p] + c->layout.llOff;
+  a.llSlotBytes = c->layout.llSlotBytes;
+  const uint64_t seq = ++c->llSeq; // parity alternates with every operation; the flag is never 0
+  a.llEpoch = (uint32_t)(seq & 0x7fffffffu) | 0x80000000u;
+  if ((a.llEpoch & 1u) != (uint32_t)(seq & 1u)) return flagcxInternalError;
+  a.flags = 0;
+  const size_t units = (bytes + 7) / 8;
+  const int nCtas = (int)std::max<size_t>(1, std::min<size_t>((units + FLAGCX_DEVICE_THREADS_PER_CTA - 1) / FLAGCX_DEVICE_THREADS_PER_CTA, 16));
+  if (c->emu) return emuSubmit(c, kFamLl, &a, nullptr, nCtas, stream);
+  LaunchCtx lc;
+  lc.comm = &c->dev;
+  lc.stream = stream;
+  lc.nCtas = nCtas;
+  cudaError_t e = launchLlKernel(lc, a);
+  if (e != cudaSuccess) {
+    FCX_WARN("LL kernel launch failed: %s", cudaGetErrorString(e));
+    return flagcxUnhandledDeviceError;
+  }
+  return flagcxSuccess;
+}
+
 // ---------------------------------------------------------------------------
 flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_t stream) {
   const int n = c->nranks;
@@ -308,6 +356,21 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   FCXCHECK(setReduceEpilogue(c, a, rq));
   const size_t es = a.elemSize, oes = outElemSize(a);
   const size_t count = rq.count;
+  // Small messages: no barrier, no registration, any buffer.  The choice depends only on
+  // what every rank knows (size, type, settings, tuner table), so all ranks agree on it.
+  {
+    TuneChoice pre = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, true, false);
+    const int want = rq.algo >= 0 ? rq.algo : pre.algo;
+    if (want == FLAGCX_ALGO_LL && n > 1 && count > 0 && a.outMode == kOutSame && !a.residual &&
+        count * es <= c->layout.llSlotBytes / 2) {
+      a.kind = kLlAllReduce;
+      a.count = count;
+      setIn(c, a, BufView(), rq.send);
+      setOut(c, a, BufView(), rq.recv);
+      note(c, flagcxCommOpAllReduce, count * es, FLAGCX_ALGO_LL, 0);
+      return launchLl(c, a, count * es, stream);
+    }
+  }
   UserBuf uin, uout;
   FCXCHECK(resolve(c, rq.send, count * es, 0, stream, &uin));
   if (rq.send == rq.recv) uout = uin; // in place stays in place, stand-in included
@@ -317,8 +380,9 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   TuneChoice ch = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, inVis && outVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if ((algo == FLAGCX_ALGO_NVLS_ONESHOT || algo == FLAGCX_ALGO_NVLS_TWOSHOT) && !nvlsOk) algo = FLAGCX_ALGO_TWOSHOT;
+  if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_ONESHOT; // not eligible above
   if (algo != FLAGCX_ALGO_ONESHOT && algo != FLAGCX_ALGO_TWOSHOT && algo != FLAGCX_ALGO_NVLS_ONESHOT &&
-      algo != FLAGCX_ALGO_NVLS_TWOSHOT)
+      algo != FLAGCX_ALGO_NVLS_TWOSHOT && algo != FLAGCX_ALGO_RING)
     algo = FLAGCX_ALGO_TWOSHOT;
   // one-shot writes its output while peers may still read the same addresses
   if (algo == FLAGCX_ALGO_ONESHOT && uin.local == uout.local && inVis) algo = FLAGCX_ALGO_TWOSHOT;
@@ -354,6 +418,45 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       applyOutLocal(c, a, uout, off * oes);
       a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
       FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
+      if (count == 0) break;
+    }
+    return finishOut(uout, stream);
+  }
+
+  // ring: reduce-scatter round the ring into the output, then all-gather round the ring
+  if (algo == FLAGCX_ALGO_RING && n > 1 && a.outMode == kOutSame && !a.residual && outVis) {
+    a.kind = kAllReduceRing;
+    CollArgs probe = a;
+    const size_t slot = setRing(c, probe, es, 0);
+    const size_t perLaunch = slot * (size_t)n;
+    for (size_t off = 0; off < count || off == 0; off += perLaunch) {
+      const size_t cnt = std::min(perLaunch, count - off);
+      a.count = cnt;
+      a.xchg = 0;
+      setRing(c, a, es, 2 * (n - 1));
+      setIn(c, a, BufView(), uin.local, off * es); // only this rank reads its input
+      applyOut(c, a, uout, off * oes);
+      FCXCHECK(launch(c, kFamReduce, a, nCtas, stream));
+      if (count == 0) break;
+    }
+    return finishOut(uout, stream);
+  }
+  if (algo == FLAGCX_ALGO_RING) algo = FLAGCX_ALGO_TWOSHOT;
+
+  // two-shot with a widening result: 16-bit values cross NVLink in both phases
+  if (!nvlsAlgo && a.outMode == kOutFloat && inVis && n > 1) {
+    a.kind = kAllReduceTwoShotCast;
+    for (int p = 0; p < n; ++p) a.aux[p] = (char *)c->internalWin->peer[p] + c->layout.stagingOff;
+    // one launch reduces n slices of at most the scratch size
+    const size_t perLaunch = S / es / 16 * 16 * (size_t)n;
+    for (size_t off = 0; off < count || off == 0; off += perLaunch) {
+      const size_t cnt = std::min(perLaunch, count - off);
+      a.count = cnt;
+      a.xchg = 0;
+      applyIn(c, a, uin, off * es);
+      applyOutLocal(c, a, uout, off * oes);
+      a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
+      FCXCHECK(launch(c, kFamReduce, a, nCtas, stream));
       if (count == 0) break;
     }
     return finishOut(uout, stream);
@@ -419,6 +522,20 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PULL;
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpReduceScatter, count * es * n, algo, nCtas);
+  if (algo == FLAGCX_ALGO_RING && n > 1 && a.outMode == kOutSame && !a.residual) {
+    // neighbours only ever write into each other's scratch: no buffer needs to be visible
+    a.kind = kReduceScatterRing;
+    CollArgs probe = a;
+    const size_t slot = setRing(c, probe, es, 0);
+    if (count <= slot) {
+      a.count = count;
+      setRing(c, a, es, n - 1);
+      setIn(c, a, BufView(), uin.local);
+      setOut(c, a, BufView(), rq.recv);
+      return launch(c, kFamReduce, a, nCtas, stream);
+    }
+    algo = FLAGCX_ALGO_PULL; // blocks larger than a scratch slot take the direct path
+  }
   if (inVis) {
     a.kind = algo == FLAGCX_ALGO_NVLS ? kReduceScatterNvls : kReduceScatter;
     a.count = count;
@@ -509,13 +626,25 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   const bool sendEverywhere = rq.op != flagcxCommOpBroadcast && rq.op != flagcxCommOpScatter;
   const bool recvEverywhere = rq.op != flagcxCommOpGather;
   const bool iAmRoot = me == rq.root;
+  if (rq.op == flagcxCommOpAllGather && n > 1 && blk > 0 && blk <= c->layout.llSlotBytes / 2) {
+    TuneChoice pre = c->tuner->choose(rq.op, recvBytes, n, true, false);
+    if ((rq.algo >= 0 ? rq.algo : pre.algo) == FLAGCX_ALGO_LL) {
+      a.kind = kLlAllGather;
+      a.count = blk;
+      a.outStride = blk;
+      setIn(c, a, BufView(), rq.send);
+      setOut(c, a, BufView(), rq.recv);
+      note(c, rq.op, recvBytes, FLAGCX_ALGO_LL, 0);
+      return launchLl(c, a, blk, stream);
+    }
+  }
   UserBuf uin, uout;
   if (sendEverywhere) FCXCHECK(resolve(c, rq.send, sendBytes, 0, stream, &uin));
   if (recvEverywhere) FCXCHECK(resolve(c, rq.recv, recvBytes, 1, stream, &uout));
   bool inVis = uin.visible(), outVis = uout.visible();
   // Scatter has no argument that every rank owns: with run-time pointer exchange the
   // root alone publishes its input and the others learn it.
-  const bool exchanging = c->emu ? getEnv("FLAGCX_EMU_EXCHANGE") != nullptr : c->exportUserBuffers;
+  const bool exchanging = c->emu ? getEnv("FLAGCX_EMU_EXCHANGE") != nullptr : c->autoExport;
   bool scatterExchange = false;
   if (rq.op == flagcxCommOpScatter && exchanging && n > 1) {
     if (iAmRoot) {
@@ -541,6 +670,9 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   TuneChoice ch = c->tuner->choose(rq.op, std::max(sendBytes, recvBytes), n, inVis || outVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PUSH;
+  if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_PUSH; // not eligible above
+  const bool ringWanted = algo == FLAGCX_ALGO_RING && rq.op == flagcxCommOpAllGather && n > 1;
+  if (algo == FLAGCX_ALGO_RING) algo = FLAGCX_ALGO_PUSH;
   if (algo == FLAGCX_ALGO_PUSH && !(outVis && pushKind >= 0)) algo = FLAGCX_ALGO_PULL;
   if (algo == FLAGCX_ALGO_PULL && !inVis && outVis && pushKind >= 0) algo = FLAGCX_ALGO_PUSH; // avoids staging
   if (algo != FLAGCX_ALGO_PUSH && algo != FLAGCX_ALGO_NVLS) algo = FLAGCX_ALGO_PULL;
@@ -556,6 +688,17 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
     setIn(c, a, BufView(), rq.send);
     setOut(c, a, uout.view, rq.recv);
     return launch(c, kFamNvls, a, nCtas, stream);
+  }
+  if (ringWanted && outVis) {
+    a.kind = kAllGatherRing;
+    a.count = blk;
+    a.inStride = blk;
+    a.outStride = blk;
+    setRing(c, a, 1, n - 1);
+    setIn(c, a, BufView(), rq.send);
+    applyOut(c, a, uout);
+    FCXCHECK(launch(c, kFamCopy, a, nCtas, stream));
+    return finishOut(uout, stream);
   }
   if (algo == FLAGCX_ALGO_PUSH) {
     a.kind = pushKind;
@@ -618,7 +761,7 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   // exported gets a stand-in inside resolve().
   UserBuf uin;
   FCXCHECK(resolve(c, rq.send, sendSpan, 0, stream, &uin));
-  if (!rq.send && c->exportUserBuffers) uin.reach = kReachExport; // nothing to send: publish a null pointer
+  if (!rq.send && c->autoExport) uin.reach = kReachExport; // nothing to send: publish a null pointer
   if (uin.visible()) {
     CollArgs a;
     initArgs(c, a, kAllToAllvPull, rq.dtype);
@@ -630,7 +773,10 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
     }
     applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
-    TuneChoice ch = c->tuner->choose(flagcxCommOpAlltoAllv, total, n, true, false);
+    // Every rank must launch the same grid (CTA b meets CTA b of its peers), but the byte
+    // counts differ from rank to rank: the count cannot follow the size here.
+    TuneChoice ch;
+    ch.nCtas = (int)readParam("ALLTOALLV_CTAS", 16);
     const int nCtas = pickCtas(c, rq, ch);
     note(c, flagcxCommOpAlltoAllv, total, FLAGCX_ALGO_PULL, nCtas);
     return launch(c, kFamCopy, a, nCtas, stream);

@@ -203,8 +203,10 @@ flagcxResult_t emuSubmit(flagcxComm *c, int family, const CollArgs *coll, const 
     CollArgs *d = w->dColl + (size_t)slot * n;
     FCX_CUDACHECK(cudaMemcpyAsync(d, w->coll.data(), sizeof(CollArgs) * n, cudaMemcpyHostToDevice, stream));
     lc.emuArgs = d;
-    e = family == 0 ? launchReduceKernel(lc, w->coll[0], n) : family == 1 ? launchCopyKernel(lc, w->coll[0])
-                                                                          : cudaErrorNotSupported;
+    e = family == 0   ? launchReduceKernel(lc, w->coll[0], n)
+        : family == 1 ? launchCopyKernel(lc, w->coll[0])
+        : family == 4 ? launchLlKernel(lc, w->coll[0])
+                      : cudaErrorNotSupported;
   }
   if (e != cudaSuccess) {
     FCX_WARN("emulated-world launch failed: %s", cudaGetErrorString(e));

@@ -288,7 +288,7 @@ void RegCache::closeAtPeers(const Entry &e) {
   }
 }
 
-bool RegCache::lookup(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS]) {
+bool RegCache::find(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS], bool exportNew) {
   if (!running_.load() || !p) return false;
   void *base = nullptr;
   size_t size = 0;
@@ -305,6 +305,7 @@ bool RegCache::lookup(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS
     it = entries_.end();
   }
   if (it == entries_.end()) {
+    if (!exportNew) return false;
     Entry e;
     e.base = base;
     e.size = size;

@@ -69,7 +69,9 @@ class RegCache {
   // Addresses of [p, p+bytes) as seen by each peer (peerVa[rank] = p).  Returns
   // false when the allocation cannot be exported (not a cudaMalloc block, a peer
   // failed to open it); the verdict is cached per allocation.
-  bool lookup(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS]);
+  bool lookup(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS]) { return find(p, bytes, peerVa, true); }
+  // The same, but an allocation that has not been exported yet stays that way.
+  bool lookupKnown(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS]) { return find(p, bytes, peerVa, false); }
   // Forgets the allocation that contains p (and has every peer unmap it).
   void forget(const void *p);
 
@@ -87,6 +89,7 @@ class RegCache {
   struct Request { uint32_t op, srcRank; uint64_t va; unsigned char handle[kIpcHandleBytes]; };
   struct Reply { uint64_t va; };
 
+  bool find(const void *p, size_t bytes, void *peerVa[FLAGCX_MAX_RANKS], bool exportNew);
   void serve();
   bool handle(int fd);
   int peerFd(int peer);

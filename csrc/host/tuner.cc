@@ -11,7 +11,10 @@
 
 namespace fcx {
 
-FCX_PARAM(MaxCtas, "MAX_CTAS", 48)
+// Past about 32 CTAs (512 threads each) a B200 pair gains nothing: 590 GB/s at 32,
+// 500-600 at 48 and 96 (all-gather and reduce-scatter of 436 MB), and every extra CTA is
+// an SM that a GEMM running beside the collective does not get.
+FCX_PARAM(MaxCtas, "MAX_CTAS", 32)
 FCX_PARAM(OneShotMaxBytes, "ONESHOT_MAX_BYTES", 0)
 
 int Tuner::bucketOf(size_t bytes) {
@@ -28,11 +31,18 @@ flagcxResult_t Tuner::init(flagcxComm *c) {
   maxCtas = (int)std::max<int64_t>(1, std::min<int64_t>(readParam("MAX_CTAS", paramMaxCtas()), FLAGCX_COLL_BARRIER_SLOTS));
   forcedCtas = (int)readParam("NCTAS", 0);
   forcedAlgo = FLAGCX_ALGO_AUTO;
+  {
+    const size_t cap = c->layout.llSlotBytes / 2;
+    const int64_t ar = readParam("LL_MAX_BYTES", c->nranks <= 2 ? (64 << 10) : c->nranks <= 4 ? (32 << 10) : (16 << 10));
+    const int64_t ag = readParam("LL_ALLGATHER_MAX_BYTES", 8 << 10); // per-rank block
+    llMaxAllReduce = c->nranks > 1 ? (size_t)std::max<int64_t>(0, std::min<int64_t>(ar, (int64_t)cap)) : 0;
+    llMaxAllGather = c->nranks > 1 ? (size_t)std::max<int64_t>(0, std::min<int64_t>(ag, (int64_t)cap)) : 0;
+  }
   if (const char *s = getEnv("FLAGCX_ALGO")) {
     static const struct { const char *n; int v; } names[] = {
         {"oneshot", FLAGCX_ALGO_ONESHOT}, {"twoshot", FLAGCX_ALGO_TWOSHOT},
         {"nvls_oneshot", FLAGCX_ALGO_NVLS_ONESHOT}, {"nvls_twoshot", FLAGCX_ALGO_NVLS_TWOSHOT},
-        {"push", FLAGCX_ALGO_PUSH}, {"pull", FLAGCX_ALGO_PULL}, {"nvls", FLAGCX_ALGO_NVLS}};
+        {"push", FLAGCX_ALGO_PUSH}, {"pull", FLAGCX_ALGO_PULL}, {"nvls", FLAGCX_ALGO_NVLS}, {"ll", FLAGCX_ALGO_LL}, {"ring", FLAGCX_ALGO_RING}};
     for (auto &e : names)
       if (!strcasecmp(s, e.n)) forcedAlgo = e.v;
   }
@@ -50,7 +60,10 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       size_t oneShotMax = paramOneShotMaxBytes() > 0 ? (size_t)paramOneShotMaxBytes()
                           : nranks <= 2 ? (8u << 20) : nranks <= 4 ? (512u << 10) : (256u << 10);
       // with two ranks the switch saves no traffic over a plain peer read
-      if (nvlsOk && nranks > 2) ch.algo = bytes < (1u << 20) ? FLAGCX_ALGO_NVLS_ONESHOT : FLAGCX_ALGO_NVLS_TWOSHOT;
+      // every rank sends its whole input to every peer in the LL path, so its range shrinks
+      // as the world grows
+      if (bytes <= llMaxAllReduce) ch.algo = FLAGCX_ALGO_LL;
+      else if (nvlsOk && nranks > 2) ch.algo = bytes < (1u << 20) ? FLAGCX_ALGO_NVLS_ONESHOT : FLAGCX_ALGO_NVLS_TWOSHOT;
       else ch.algo = bytes <= oneShotMax ? FLAGCX_ALGO_ONESHOT : FLAGCX_ALGO_TWOSHOT;
       if (ch.algo == FLAGCX_ALGO_TWOSHOT || ch.algo == FLAGCX_ALGO_NVLS_TWOSHOT) work = bytes / std::max(1, nranks);
       break;
@@ -60,6 +73,9 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       work = bytes / std::max(1, nranks);
       break;
     case flagcxCommOpAllGather:
+      if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
+      ch.algo = FLAGCX_ALGO_PUSH;
+      break;
     case flagcxCommOpBroadcast:
     case flagcxCommOpAlltoAll:
       ch.algo = FLAGCX_ALGO_PUSH; // the launcher falls back to pull when the output is not registered
@@ -72,8 +88,11 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
   // work per CTA below which another CTA costs more (its barrier flags on every peer)
   // than it brings; the offline tuner on B200 pairs picked 8 CTAs for 1-2 MiB
   static const size_t perCta = (size_t)std::max<int64_t>(1024, readParam("BYTES_PER_CTA", 64 << 10));
-  // bandwidth-bound sizes get twice the CTAs: more NVLink accesses in flight
-  size_t cap = work >= (16u << 20) ? std::min<size_t>(2 * (size_t)maxCtas, FLAGCX_COLL_BARRIER_SLOTS) : (size_t)maxCtas;
+  // all-to-all moves n separate streams per CTA and keeps gaining up to about 96 CTAs
+  // (365 GB/s at 32, 616 at 96 on a B200 pair, 1 GiB); everything else is flat beyond 32
+  size_t cap = op == flagcxCommOpAlltoAll && work >= (16u << 20)
+                   ? std::min<size_t>(3 * (size_t)maxCtas, FLAGCX_COLL_BARRIER_SLOTS)
+                   : (size_t)maxCtas;
   ch.nCtas = (int)std::max<size_t>(1, std::min<size_t>((work + perCta - 1) / perCta, cap));
   return ch;
 }
@@ -164,7 +183,8 @@ namespace {
 
 struct Candidate { int algo, nCtas; };
 
-std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, bool registered, bool nvls, int maxCtas) {
+std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, bool registered, bool nvls, int maxCtas,
+                                     size_t llCap) {
   std::vector<int> algos;
   switch (op) {
     case flagcxCommOpAllReduce:
@@ -174,14 +194,17 @@ std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, boo
         if (bytes <= (16u << 20)) algos.push_back(FLAGCX_ALGO_NVLS_ONESHOT);
         algos.push_back(FLAGCX_ALGO_NVLS_TWOSHOT);
       }
+      if (bytes >= (1u << 20)) algos.push_back(FLAGCX_ALGO_RING);
       break;
     case flagcxCommOpReduceScatter:
       algos.push_back(FLAGCX_ALGO_PULL);
+      if (bytes >= (1u << 20)) algos.push_back(FLAGCX_ALGO_RING);
       if (nvls && registered) algos.push_back(FLAGCX_ALGO_NVLS);
       break;
     case flagcxCommOpAllGather:
       if (registered) algos.push_back(FLAGCX_ALGO_PUSH);
       algos.push_back(FLAGCX_ALGO_PULL);
+      if (registered && bytes >= (1u << 20)) algos.push_back(FLAGCX_ALGO_RING);
       if (nvls && registered) algos.push_back(FLAGCX_ALGO_NVLS);
       break;
     case flagcxCommOpAlltoAll:
@@ -198,7 +221,9 @@ std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, boo
       if (ctas > 1 && (size_t)ctas * 4096 > bytes) continue;
       out.push_back({a, ctas});
     }
-  (void)n;
+  // the barrier-free path picks its own CTA count
+  if (n > 1 && ((op == flagcxCommOpAllReduce && bytes <= llCap) || (op == flagcxCommOpAllGather && bytes / n <= llCap)))
+    out.push_back({FLAGCX_ALGO_LL, 1});
   return out;
 }
 
@@ -250,7 +275,7 @@ flagcxResult_t Tuner::tune(flagcxComm *c, flagcxCommOp_t op, flagcxDataType_t dt
       rq.count = (op == flagcxCommOpAllReduce) ? elems : std::max<size_t>(1, elems / n);
       const bool nvlsOk = c->nvls && registered && ws->mc && wr->mc && (rq.count * es) % 16 == 0;
       TuneChoice base = heuristic(op, bytes, n, registered, nvlsOk);
-      auto cands = candidatesFor(op, bytes, n, registered, nvlsOk, tuneMaxCtas);
+      auto cands = candidatesFor(op, bytes, n, registered, nvlsOk, tuneMaxCtas, c->layout.llSlotBytes / 2);
       cands.push_back({base.algo, base.nCtas});
       float bestUs = 0, baseUs = 0;
       Candidate best{base.algo, base.nCtas};

@@ -44,6 +44,9 @@ struct Tuner {
   int maxCtas = 32;
   int forcedAlgo = FLAGCX_ALGO_AUTO; // FLAGCX_ALGO
   int forcedCtas = 0;                // FLAGCX_NCTAS
+  // largest messages the heuristic sends down the barrier-free LL path
+  // (FLAGCX_LL_MAX_BYTES, FLAGCX_LL_ALLGATHER_MAX_BYTES; 0 switches it off)
+  size_t llMaxAllReduce = 0, llMaxAllGather = 0;
 };
 
 } // namespace fcx

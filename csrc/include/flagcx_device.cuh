@@ -28,6 +28,10 @@
 #define FLAGCX_BARRIER_SLOTS (FLAGCX_COLL_BARRIER_SLOTS + FLAGCX_USER_BARRIER_SLOTS)
 #define FLAGCX_MAX_SIGNALS 1024
 #define FLAGCX_MAX_COUNTERS 256
+/* signals [512, 512+320): arrival counters of the multicast barrier (flagcxDevBarrierNvls),
+ * 256 for the library's kernels (one per CTA slot) and 64 for users */
+#define FLAGCX_NVLS_BARRIER_SIGNAL_BASE 512
+#define FLAGCX_NVLS_USER_BARRIER_SLOTS 64
 
 #define FLAGCX_DEVICE_CTA_COUNT 32
 #define FLAGCX_DEVICE_THREADS_PER_CTA 512
@@ -69,6 +73,8 @@ struct flagcxDevComm {
   flagcxDevStatus *status;
   unsigned long long timeoutNs;
   int nSignals, nCounters;
+  int nvlsBarrier; /* 1: the library's kernels meet through the multicast barrier */
+  int reserved;
 };
 
 struct flagcxDevMem {
@@ -322,6 +328,33 @@ struct flagcxDevBarrierIntra {
 };
 /* One NVLink domain: the world barrier is the intra barrier. */
 typedef flagcxDevBarrierIntra flagcxDevBarrierWorld;
+
+/* ---- the same barrier through the NVLink switch ------------------------------------
+ * Needs the communicator's multicast binding (comm.mcSignalPad != NULL).  Arriving is ONE
+ * multimem.red: the switch adds 1 to the slot's counter in every rank's memory at once,
+ * instead of one store per peer; a rank waits until its own copy has grown by nRanks.
+ * Slot `index` < 256 + FLAGCX_NVLS_USER_BARRIER_SLOTS; slots from 256 on are for users.
+ * The number of completed rounds lives in the slot's signal shadow.  Block groups only. */
+struct flagcxDevBarrierNvls {
+  const flagcxDevComm &c;
+  int sig;
+  __device__ flagcxDevBarrierNvls(const flagcxDevComm &comm, int index)
+      : c(comm), sig(FLAGCX_NVLS_BARRIER_SIGNAL_BASE + index) {}
+  template <typename Coop>
+  __device__ bool sync(Coop g) {
+    g.sync(); /* the group's earlier writes happen-before the arrival */
+    bool ok = true;
+    if (g.threadRank() == 0) {
+      const unsigned long long target = c.signalShadow[sig] + (unsigned long long)c.nRanks;
+      fcxdev::fenceSys();
+      asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(c.mcSignalPad + sig), "l"(1ull) : "memory");
+      ok = fcxdev::waitGe(c, c.signalPad[c.rank] + sig, target, FLAGCX_DEV_AT_BARRIER, 0xffffffffu);
+      c.signalShadow[sig] = target;
+    }
+    int bad = __syncthreads_or(ok ? 0 : 1);
+    return !bad;
+  }
+};
 
 /* ---- one-sided operations ------------------------------------------------------------ */
 struct flagcxDevNet_None {};

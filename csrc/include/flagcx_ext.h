@@ -22,7 +22,9 @@ typedef enum {
   FLAGCX_ALGO_PUSH = 4,         /* allgather/broadcast/alltoall: write into the peers' outputs */
   FLAGCX_ALGO_PULL = 5,         /* reduce-scatter/allgather/...: read from the peers' inputs */
   FLAGCX_ALGO_NVLS = 6,         /* reduce-scatter: multimem.ld_reduce; allgather: multimem.st */
-  FLAGCX_ALGO_COUNT = 7
+  FLAGCX_ALGO_LL = 7,           /* allreduce/allgather of small messages: data+flag stores, no barrier */
+  FLAGCX_ALGO_RING = 8,         /* allreduce/reduce-scatter/allgather in n-1 neighbour-to-neighbour steps */
+  FLAGCX_ALGO_COUNT = 9
 } flagcxAlgo_t;
 
 /* Optional work fused into the store of a reducing collective. */
@@ -91,6 +93,19 @@ typedef struct {
   uint64_t hits, exports, refused, stale, peerOpened, peerClosed;
 } flagcxUserBufferStats_t;
 flagcxResult_t flagcxCommUserBufferStats(flagcxComm_t comm, flagcxUserBufferStats_t *out);
+/* Not collective.  Has every peer unmap the exported allocation that contains ptr (nothing
+ * happens if there is none).  Call it before the allocation is freed: an allocation must
+ * not be freed while another process still has it mapped.  Allocator integrations call
+ * this from their "segment is about to be released" hook (the torch backend does); no
+ * collective of any rank may still be using the memory. */
+flagcxResult_t flagcxCommForgetUserBuffer(flagcxComm_t comm, const void *ptr);
+/* By default only buffers registered with flagcxCommRegister (by every rank) are exported;
+ * other device buffers are staged.  on != 0 exports every device buffer a collective meets.
+ * The caller then guarantees that flagcxCommForgetUserBuffer (or flagcxCommDeregister) runs
+ * before any such allocation is freed -- typically from an allocator hook.  Every rank must
+ * make the same choice before its next collective.  FLAGCX_USER_BUFFER_EXPORT=2 has the same
+ * effect from the environment; =0 switches the mechanism off altogether. */
+flagcxResult_t flagcxCommSetAutoExport(flagcxComm_t comm, int on);
 /* 1 when collectives on device buffers run as NVLink kernels, 0 on the socket path. */
 flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes);
 flagcxResult_t flagcxCommHasMulticast(flagcxComm_t comm, int *yes);

@@ -34,6 +34,9 @@ enum CollKind : int {
   kAllReduceTwoShotCast, // reduce own slice into local 16-bit scratch, then pull all slices and widen to fp32
   kLlAllReduce,          // small messages: data+flag stores into per-sender slots, no barrier
   kLlAllGather,
+  kAllGatherRing,        // n-1 steps: forward the block received in the previous step to the next rank
+  kReduceScatterRing,    // n-1 steps: add the own block to the partial sum received and pass it on
+  kAllReduceRing,        // ring reduce-scatter into the output, then ring all-gather of it
   kNumCollKinds
 };
 
@@ -84,6 +87,13 @@ struct CollArgs {
   // the 16-bit scratch that holds rank p's reduced slice.  LL kinds: rank p's slot area,
   // laid out [parity][sender][llSlotBytes].
   char *aux[FLAGCX_MAX_RANKS];
+  // ring kinds: step flags, one u64 per CTA slot, monotonic over the communicator's life.
+  // A rank raises ringNext[b] at its successor and waits on ringMine[b]; step s of this
+  // launch uses the value ringBase + s + 1.  aux[] holds each rank's partial-sum scratch
+  // (n-1 slots of ringSlotElems elements, one per step, so no slot is reused in a launch).
+  unsigned long long *ringNext, *ringMine;
+  unsigned long long ringBase;
+  size_t ringSlotElems;
   size_t llSlotBytes;
   uint32_t llEpoch;    // value of the flags of this operation (never 0)
   uint32_t llPad;

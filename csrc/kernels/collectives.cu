@@ -139,6 +139,23 @@ __device__ __forceinline__ bool mbarWaitBounded(const flagcxDevComm &c, uint64_t
 }
 
 // ---------------------------------------------------------------------------
+// flags between two ranks (ring steps, point-to-point chunks)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool ctaWaitFlag(const flagcxDevComm &c, const unsigned long long *flag,
+                                            unsigned long long want, unsigned peer) {
+  bool ok = true;
+  if (threadIdx.x == 0) ok = fcxdev::waitGe(c, flag, want, FLAGCX_DEV_AT_SIGNAL, peer);
+  return !__syncthreads_or(ok ? 0 : 1);
+}
+__device__ __forceinline__ void ctaRaiseFlag(unsigned long long *flag, unsigned long long v) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fcxdev::fenceSys();
+    fcxdev::stReleaseSys(flag, v);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // reduce family
 // ---------------------------------------------------------------------------
 template <typename T, int OP, int NR>
@@ -431,6 +448,80 @@ __device__ void widenSlice(const T *src, float *dst, size_t elems, const float *
   }
 }
 
+// One hop of a ring reduction: dst[i] = x[i] (op) y[i] over this CTA's share of `elems`
+// elements (y may be null: a plain copy), accumulating in the wider type.  `last` applies
+// the scale / integer division of the epilogue.  dst may be peer memory.
+template <typename T, int OP>
+__device__ void ringCombine(const CollArgs &a, T *dst, const T *x, const T *y, size_t elems, bool last, int b, int g) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int N = 16 / (int)sizeof(T);
+  size_t ub, ue;
+  ctaShare((elems * sizeof(T) + 15) >> 4, b, g, &ub, &ue);
+  const size_t eb = ub * N, ee = ue * N < elems ? ue * N : elems;
+  if (eb >= ee) return;
+  const bool vec = ((((uintptr_t)dst) | ((uintptr_t)x) | ((uintptr_t)y)) & 15) == 0;
+  size_t done = eb;
+  if (vec) {
+    const size_t fullEnd = ee / N * N, stride = (size_t)blockDim.x * N;
+    auto emit = [&](size_t e, uint4 vx, uint4 vy) {
+      const T *px = (const T *)&vx, *py = (const T *)&vy;
+      uint4 o;
+      T *po = (T *)&o;
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        Acc v = toAcc<T>(px[i]);
+        if (y) v = combine<OP, Acc>(v, toAcc<T>(py[i]), a.redOp);
+        if (last) v = finish<Acc>(v, a.scale, a.divisor);
+        po[i] = fromAcc<T>(v);
+      }
+      st16(dst + e, o);
+    };
+    size_t e = eb + (size_t)threadIdx.x * N;
+    for (; e + 3 * stride < fullEnd; e += 4 * stride) {
+      uint4 vx[4], vy[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        vx[u] = ldSys16(x + e + u * stride);
+        vy[u] = y ? ldSys16(y + e + u * stride) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) emit(e + u * stride, vx[u], vy[u]);
+    }
+    for (; e < fullEnd; e += stride) emit(e, ldSys16(x + e), y ? ldSys16(y + e) : make_uint4(0, 0, 0, 0));
+    done = fullEnd > eb ? fullEnd : eb;
+  }
+  for (size_t e = done + threadIdx.x; e < ee; e += blockDim.x) {
+    Acc v = toAcc<T>(ldSysElem(x + e));
+    if (y) v = combine<OP, Acc>(v, toAcc<T>(ldSysElem(y + e)), a.redOp);
+    if (last) v = finish<Acc>(v, a.scale, a.divisor);
+    dst[e] = fromAcc<T>(v);
+  }
+}
+
+// Ring reduce-scatter over blocks [blockBegin(i), blockBegin(i) + blockLen(i)) of the
+// inputs; rank r ends up with the complete block r in `result` (n-1 hops, each adding the
+// sender's own contribution to the partial sum it received).  Returns false after a
+// timed-out wait.
+template <typename T, int OP>
+__device__ bool ringReduceScatter(const flagcxDevComm &c, const CollArgs &a, size_t blockElems, size_t totalElems,
+                                  T *result, int b, int g) {
+  const int rank = c.rank, n = c.nRanks, next = (rank + 1) % n, prev = (rank + n - 1) % n;
+  const T *own = (const T *)a.in[rank];
+  auto begin = [&](int i) { size_t s = blockElems * (size_t)i; return s < totalElems ? s : totalElems; };
+  auto len = [&](int i) { size_t s = begin(i); return s + blockElems < totalElems ? blockElems : totalElems - s; };
+  T *mine = (T *)a.aux[rank], *theirs = (T *)a.aux[next];
+  for (int s = 0; s < n - 1; ++s) {
+    int ci = rank - s - 1; while (ci < 0) ci += n;
+    ringCombine<T, OP>(a, theirs + (size_t)s * a.ringSlotElems, own + begin(ci),
+                       s > 0 ? mine + (size_t)(s - 1) * a.ringSlotElems : (const T *)nullptr, len(ci), false, b, g);
+    ctaRaiseFlag(a.ringNext + b, a.ringBase + s + 1);
+    if (!ctaWaitFlag(c, a.ringMine + b, a.ringBase + s + 1, (unsigned)prev)) return false;
+  }
+  ringCombine<T, OP>(a, result, own + begin(rank), n > 1 ? mine + (size_t)(n - 2) * a.ringSlotElems : (const T *)nullptr,
+                     len(rank), true, b, g);
+  return true;
+}
+
 template <typename T, int OP, int NR>
 __device__ void reduceBody(const flagcxDevComm &c, CollArgs &a) {
   const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
@@ -471,6 +562,26 @@ __device__ void reduceBody(const flagcxDevComm &c, CollArgs &a) {
     case kReduceToRoot:
       if (rank == a.root) R::slice(a, n, 0, a.count, local, 1, 0, b, g);
       break;
+    case kReduceScatterRing:
+      if (!ringReduceScatter<T, OP>(c, a, a.count, a.count * (size_t)n, (T *)a.out[rank], b, g)) return;
+      break;
+    case kAllReduceRing: {
+      // reduce-scatter into this rank's block of its own output, then pass the finished
+      // blocks round the ring: after step s a rank holds blocks rank, rank-1, .., rank-s-1
+      const size_t s = sliceElems(a.count, n, sizeof(T));
+      auto begin = [&](int i) { size_t x = s * (size_t)i; return x < a.count ? x : a.count; };
+      auto len = [&](int i) { size_t x = begin(i); return x + s < a.count ? s : a.count - x; };
+      T *myOut = (T *)a.out[rank];
+      if (!ringReduceScatter<T, OP>(c, a, s, a.count, myOut + begin(rank), b, g)) return;
+      const int next = (rank + 1) % n, prev = (rank + n - 1) % n;
+      for (int st = 0; st < n - 1; ++st) {
+        int bi = rank - st; while (bi < 0) bi += n;
+        ringCombine<T, OP>(a, (T *)a.out[next] + begin(bi), myOut + begin(bi), (const T *)nullptr, len(bi), false, b, g);
+        ctaRaiseFlag(a.ringNext + b, a.ringBase + (n - 1) + st + 1);
+        if (!ctaWaitFlag(c, a.ringMine + b, a.ringBase + (n - 1) + st + 1, (unsigned)prev)) return;
+      }
+      break;
+    }
     case kAllReduceTwoShotCast: {
       // 16-bit inputs, fp32 result.  Sending fp32 to every peer would double the NVLink
       // bytes, so each rank rounds its reduced (and scaled) slice once to the input type
@@ -658,11 +769,16 @@ __device__ void ctaFanOut(char *const *dst, int nDst, const char *src, size_t by
   if (vec) {
     size_t ve = be >> 4;
     size_t i = ub + t;
-    for (; i + nt < ve; i += 2 * (size_t)nt) {
-      uint4 v0 = ldSys16(src + (i << 4)), v1 = ldSys16(src + ((i + nt) << 4));
+    // The stores to the peers are posted; what bounds a CTA's rate is how many local
+    // loads it keeps in flight.  Eight 16-byte loads per thread (64 KiB per CTA) let a
+    // dozen or so CTAs fill the links, which matters when GEMMs want the other SMs.
+    for (; i + 7 * (size_t)nt < ve; i += 8 * (size_t)nt) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = ldSys16(src + ((i + u * (size_t)nt) << 4));
       for (int d = 0; d < nDst; ++d) {
-        st16(dst[d] + (i << 4), v0);
-        st16(dst[d] + ((i + nt) << 4), v1);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) st16(dst[d] + ((i + u * (size_t)nt) << 4), v[u]);
       }
     }
     for (; i < ve; i += nt) {
@@ -823,6 +939,20 @@ __device__ void copyBody(const flagcxDevComm &c, CollArgs &a) {
       }
       break;
     }
+    case kAllGatherRing: {
+      // step s: pass block (rank - s) on to the next rank; own block first, then whatever
+      // arrived in the step before
+      const int next = (rank + 1) % n, prev = (rank + n - 1) % n;
+      char *mine = a.out[rank];
+      if (a.in[rank] != mine + a.outStride * rank) ctaCopyShare(mine + a.outStride * rank, a.in[rank], blk, b, g);
+      for (int s = 0; s < n - 1; ++s) {
+        int bi = rank - s; while (bi < 0) bi += n;
+        ctaCopyShare(a.out[next] + a.outStride * bi, s == 0 ? a.in[rank] : mine + a.outStride * bi, blk, b, g);
+        ctaRaiseFlag(a.ringNext + b, a.ringBase + s + 1);
+        if (!ctaWaitFlag(c, a.ringMine + b, a.ringBase + s + 1, (unsigned)prev)) return;
+      }
+      break;
+    }
     case kAllGatherPull:
       for (int k = 0; k < n; ++k) {
         int p = rank + k; if (p >= n) p -= n;
@@ -946,20 +1076,6 @@ __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
 // ---------------------------------------------------------------------------
 // grouped point-to-point (see P2pArgs)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ bool ctaWaitFlag(const flagcxDevComm &c, const unsigned long long *flag,
-                                            unsigned long long want, unsigned peer) {
-  bool ok = true;
-  if (threadIdx.x == 0) ok = fcxdev::waitGe(c, flag, want, FLAGCX_DEV_AT_SIGNAL, peer);
-  return !__syncthreads_or(ok ? 0 : 1);
-}
-__device__ __forceinline__ void ctaRaiseFlag(unsigned long long *flag, unsigned long long v) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    fcxdev::fenceSys();
-    fcxdev::stReleaseSys(flag, v);
-  }
-}
-
 __device__ void p2pBody(const flagcxDevComm &c, const P2pArgs &a) {
   const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
   const size_t slot = a.slotBytes;

@@ -110,6 +110,10 @@ __device__ __forceinline__ void ctaShare(size_t n, int b, int g, size_t *begin, 
 // ---- barrier wrapper ---------------------------------------------------------------------
 __device__ __forceinline__ bool ctaBarrier(const flagcxDevComm &c, int slot) {
   if (c.nRanks == 1) { __syncthreads(); return true; }
+  if (c.nvlsBarrier) { // one multimem.red through the switch instead of a store per peer
+    flagcxDevBarrierNvls bar(c, slot);
+    return bar.sync(flagcxCoopBlock());
+  }
   flagcxDevBarrierIntra bar(c, slot);
   return bar.sync(flagcxCoopBlock());
 }

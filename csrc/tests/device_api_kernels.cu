@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include "flagcx_device.cuh"
+#include "flagcx_device_c.cuh"
 
 namespace {
 
@@ -191,6 +192,62 @@ __global__ void kWaitTimesOut(TestArgs a) {
   if (threadIdx.x == 0) resultOf(a, c.rank)[0] = ok ? 1 : 0;
 }
 
+// 10. the C-linkage wrappers (flagcx_device_c.cuh): the same ring exchange as scenario 3
+// through flagcxDevPut_RSigAdd_LCtrInc / flagcxDevWaitSignal, a flagcxDevGet back, a
+// flagcxDevPutValue_RSigInc, shadows and the barrier, addressed only by opaque pointers.
+__global__ void kCWrappers(TestArgs a) {
+  const void *comm = &a.comms[blockIdx.y];
+  const void *mem = &a.mems[blockIdx.y];
+  const flagcxDevComm &c = a.comms[blockIdx.y];
+  const int half = a.nWords / 2, n = c.nRanks;
+  const int next = (c.rank + 1) % n, prev = (c.rank + n - 1) % n;
+  const flagcxDevSignal_t sigData = 20, sigValue = 21;
+  const flagcxDevCounter_t ctr = 7;
+  unsigned long long *mine = (unsigned long long *)flagcxGetLocalPointer(a.mems[blockIdx.y], 0);
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    flagcxDevResetSignal(comm, 0, sigData);
+    flagcxDevResetSignal(comm, 0, sigValue);
+    flagcxDevResetCounter(comm, 0, ctr);
+  }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) mine[i] = (unsigned long long)c.rank * 100000 + i;
+  for (int i = half + threadIdx.x; i < a.nWords; i += blockDim.x) mine[i] = 0;
+  flagcxDevBarrierSync(comm, FLAGCX_TEAM_WORLD, 9, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_ACQ_REL, FLAGCX_MEMORY_SCOPE_SYSTEM);
+  // first quarter to the next rank's second half, signal += 5, local counter += 1
+  const size_t q = (size_t)(half / 2) * 8;
+  flagcxDevPut_RSigAdd_LCtrInc(comm, mem, (size_t)half * 8, mem, 0, q, FLAGCX_TEAM_WORLD, next, 0, FLAGCX_COOP_BLOCK,
+                               FLAGCX_MEMORY_SCOPE_SYSTEM, FLAGCX_MEMORY_ORDER_RELEASE, sigData, 5, ctr);
+  flagcxDevWaitSignal(comm, sigData, 5, 64, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_ACQUIRE);
+  flagcxDevWaitCounter(comm, ctr, 1, 64, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_ACQUIRE);
+  for (int i = threadIdx.x; i < half / 2; i += blockDim.x)
+    ok = ok && mine[half + i] == (unsigned long long)prev * 100000 + i;
+  ok = ok && flagcxDevReadSignal(comm, sigData, 64, 0, FLAGCX_MEMORY_ORDER_ACQUIRE) == 5 &&
+       flagcxDevReadCounter(comm, ctr, 64, 0, FLAGCX_MEMORY_ORDER_ACQUIRE) == 1;
+  // warp 0 fetches the second quarter of the previous rank's first half, all but its last
+  // word: the buffer's last word is the target of the putValue below
+  if (threadIdx.x < 32)
+    flagcxDevGet(comm, mem, q, mem, (size_t)half * 8 + q, q - 8, FLAGCX_TEAM_INTRA, prev, 0, FLAGCX_COOP_WARP,
+                 FLAGCX_MEMORY_SCOPE_SYSTEM, FLAGCX_MEMORY_ORDER_ACQUIRE);
+  __syncthreads();
+  for (int i = threadIdx.x; i < half / 2 - 1; i += blockDim.x)
+    ok = ok && mine[half + half / 2 + i] == (unsigned long long)prev * 100000 + half / 2 + i;
+  // one thread writes a value into the next rank's last word and raises a signal; the
+  // receiver waits for "one more than its shadow"
+  if (threadIdx.x == 0) {
+    flagcxDevIncreaseSignalShadow(comm, 0, sigValue, 1);
+    flagcxDevPutValue_RSigInc(comm, mem, (size_t)(a.nWords - 1) * 8, 0xabc000ull + c.rank, FLAGCX_TEAM_WORLD, next, 0,
+                              FLAGCX_COOP_THREAD, FLAGCX_MEMORY_SCOPE_SYSTEM, FLAGCX_MEMORY_ORDER_RELEASE, sigValue);
+    flagcxDevWaitSignalMeetShadow(comm, 0, sigValue, 64, FLAGCX_COOP_THREAD, FLAGCX_MEMORY_ORDER_ACQUIRE);
+    ok = ok && fcxdev::ldRelaxedSys(mine + a.nWords - 1) == 0xabc000ull + prev;
+  }
+  flagcxDevFlush(comm, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_RELEASE);
+  // split barrier: nobody leaves before everyone has checked
+  flagcxDevBarrierArrive(comm, FLAGCX_TEAM_WORLD, 9, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_RELEASE, FLAGCX_MEMORY_SCOPE_SYSTEM);
+  flagcxDevBarrierWait(comm, FLAGCX_TEAM_WORLD, 9, 0, FLAGCX_COOP_BLOCK, FLAGCX_MEMORY_ORDER_ACQUIRE, FLAGCX_MEMORY_SCOPE_SYSTEM);
+  int good = __syncthreads_and(ok ? 1 : 0);
+  if (threadIdx.x == 0) resultOf(a, c.rank)[0] = good;
+}
+
 } // namespace
 
 extern "C" int fcxDevTestSizes(int *devCommBytes, int *devMemBytes) {
@@ -228,6 +285,7 @@ extern "C" int fcxDevTestLaunch(int which, const void *dComms, const void *dMems
     case 7: fn = (const void *)kTeams; break;
     case 8: fn = (const void *)kReset; break;
     case 9: fn = (const void *)kWaitTimesOut; break;
+    case 10: fn = (const void *)kCWrappers; break;
     default: return (int)cudaErrorInvalidValue;
   }
   return (int)cudaLaunchCooperativeKernel(fn, dim3(1, nRanks), dim3(256), params, 0, (cudaStream_t)stream);

@@ -73,7 +73,7 @@ def _make_layer_fn(cfg: LlamaConfig):
         attn_norm, wqkv, wo, ffn_norm, w13, w2 = params
         T = x.shape[0]
         h = ops.rmsnorm(x, attn_norm, cfg.eps)
-        qkv = F.linear(h, wqkv)
+        qkv = ops.linear(h, wqkv)
         q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
         q = ops.rope(q.reshape(T, nh, hd), cfg.rope_theta)
         k = ops.rope(k.reshape(T, nkv, hd), cfg.rope_theta)
@@ -81,9 +81,9 @@ def _make_layer_fn(cfg: LlamaConfig):
         a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
                                            v.transpose(0, 1).unsqueeze(0), is_causal=True, enable_gqa=True)
         a = a.squeeze(0).transpose(0, 1).reshape(T, nh * hd)
-        x = x + F.linear(a, wo)
+        x = x + ops.linear(a, wo)
         h = ops.rmsnorm(x, ffn_norm, cfg.eps)
-        x = x + F.linear(ops.swiglu(F.linear(h, w13)), w2)
+        x = x + ops.linear(ops.swiglu(ops.linear(h, w13)), w2)
         return x
 
     return layer
@@ -93,7 +93,7 @@ def _make_head_fn(cfg: LlamaConfig):
     def head(params, x, targets):
         norm, w = params
         h = ops.rmsnorm(x, norm, cfg.eps)
-        logits = F.linear(h, w)
+        logits = ops.linear(h, w)
         return ops.cross_entropy_(logits, targets)
 
     return head

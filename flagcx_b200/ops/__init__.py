@@ -102,6 +102,39 @@ def swiglu(ab: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(ab)
 
 
+class _LinearInto(torch.autograd.Function):
+    """y = x @ w.T whose weight gradient is written by the GEMM itself into a buffer the
+    caller owns (a slice of a flat gradient buffer), instead of into a fresh tensor that
+    would then be copied there.  `sink` is (destination [out, in], callback run once the
+    GEMM is queued); the weight's .grad stays None."""
+
+    @staticmethod
+    def forward(ctx, x, w, sink):
+        ctx.save_for_backward(x, w)
+        ctx.sink = sink
+        return torch.nn.functional.linear(x, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        dst, done = ctx.sink
+        dx = g.matmul(w) if ctx.needs_input_grad[0] else None
+        torch.mm(g.reshape(-1, g.shape[-1]).t(), x.reshape(-1, x.shape[-1]), out=dst)
+        done()
+        return dx, None, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """F.linear; if the weight carries a `_grad_sink` its gradient goes straight there."""
+    sink = getattr(w, "_grad_sink", None)
+    if sink is None:
+        return torch.nn.functional.linear(x, w)
+    return _LinearInto.apply(x, w, sink)
+
+
+_unit_grad_checked = False
+
+
 class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, targets):
@@ -109,20 +142,27 @@ class _CrossEntropy(torch.autograd.Function):
         rows = logits.numel() // logits.size(-1)
         losses = ext().cross_entropy_fwd_bwd_(logits, targets, 1.0 / rows)
         _count()
+        # tell autograd the input was overwritten (it then refuses a backward of an
+        # upstream op that had saved these logits); a dirty input must also be an output
+        ctx.mark_dirty(logits)
         ctx.save_for_backward(logits)
-        return losses.mean()
+        return losses.mean(), logits
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, g, _unused):
+        global _unit_grad_checked
         (dlogits,) = ctx.saved_tensors
         if assume_unit_loss_grad:
+            if not _unit_grad_checked:  # one synchronising look, the first time only
+                assert float(g) == 1.0, "assume_unit_loss_grad is set but the loss was differentiated with another gradient"
+                _unit_grad_checked = True
             return dlogits, None  # loss.backward() with the default gradient of 1
         return dlogits.mul_(g.to(dlogits.dtype)), None
 
 
 def cross_entropy_(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Mean softmax cross-entropy.  Consumes `logits` (it is overwritten with the gradient)."""
-    return _CrossEntropy.apply(logits, targets)
+    return _CrossEntropy.apply(logits, targets)[0]
 
 
 def adamw_flat_(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step) -> None:

@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 
+#include <atomic>
+
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -26,8 +28,10 @@ constexpr int kMaxDevices = 64;
 // be read (and tested) like the allocating variant.
 static __device__ __align__(256) float gPartialScratch[FLAGCX_NOALLOC_RMSNORM_MAX_CTAS * FLAGCX_NOALLOC_RMSNORM_MAX_HIDDEN];
 
-// Device address of gPartialScratch per device, filled on the first call there.
-float *gScratchAddr[kMaxDevices] = {};
+// Device address of gPartialScratch per device, filled on the first call there.  Atomic:
+// two host threads may make that first call at once; both look the address up and store
+// the same value.
+std::atomic<float *> gScratchAddr[kMaxDevices];
 
 __device__ __forceinline__ float warpSum(float v) {
 #pragma unroll
@@ -145,19 +149,28 @@ extern "C" int flagcxRmsnormBwdNoAlloc(const void *g, const void *x, const void 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
-  if (!gScratchAddr[dev]) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (s) {
+    // the scratch address used below belongs to the current device: the stream must too
+    int sdev = -1;
+    e = cudaStreamGetDevice(s, &sdev);
+    if (e != cudaSuccess) return (int)e;
+    if (sdev != dev) {
+      fprintf(stderr, "flagcxRmsnormBwdNoAlloc: the stream belongs to device %d but device %d is current\n", sdev, dev);
+      return (int)cudaErrorInvalidValue;
+    }
+  }
+  float *scratch = gScratchAddr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // once per device, with that device current: the array's name is a host-side
     // stand-in, the kernels need its device address
-    float *p = nullptr;
-    e = cudaGetSymbolAddress((void **)&p, gPartialScratch);
+    e = cudaGetSymbolAddress((void **)&scratch, gPartialScratch);
     if (e != cudaSuccess) {
       fprintf(stderr, "flagcxRmsnormBwdNoAlloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
       return (int)e;
     }
-    gScratchAddr[dev] = p;
+    gScratchAddr[dev].store(scratch, std::memory_order_release);
   }
-  float *scratch = gScratchAddr[dev];
-  cudaStream_t s = (cudaStream_t)stream;
   int ctas = rows < FLAGCX_NOALLOC_RMSNORM_MAX_CTAS ? (int)rows : FLAGCX_NOALLOC_RMSNORM_MAX_CTAS;
   if (ctas < 1) ctas = 1;
   bwdKernel<<<ctas, kThreads, 0, s>>>((const bf16 *)g, (const bf16 *)x, (const bf16 *)w, rstd, (bf16 *)dx, scratch, rows,

@@ -20,12 +20,18 @@
  * FLAGCX_NOALLOC_RMSNORM_MAX_HIDDEN; larger sizes are refused with
  * cudaErrorInvalidValue and a message on stderr.  The scratch array is
  * FLAGCX_NOALLOC_RMSNORM_MAX_CTAS x FLAGCX_NOALLOC_RMSNORM_MAX_HIDDEN floats (4 MiB)
- * of device memory that every GPU which loads this library holds until the process
- * exits, whether or not the entry point is ever called.
+ * of device memory that every GPU which loads this library's device code holds until
+ * the process exits.  With CUDA's default lazy module loading the array comes into
+ * being when the module is first used on a device, which is the first call of this
+ * entry point there: that one call may therefore make the driver set the 4 MiB aside,
+ * every later call touches no allocator at all.  So make one warm-up call per device
+ * at start-up, before the memory budget is fixed.
  *
- * The first call on each device looks up the device address of that array (one
- * cudaGetSymbolAddress, no allocation).  Make that first call outside any stream
- * capture.  All calls on a device share the one array, and it keeps whatever the
+ * The first call on each device also looks up the device address of that array (one
+ * cudaGetSymbolAddress) and keeps it for the life of the process; after
+ * cudaDeviceReset() on that device the kept address is stale and the entry point must
+ * not be used again in the process.  Make the first call outside any stream capture.
+ * A non-NULL stream must belong to the current device.  All calls on a device share the one array, and it keeps whatever the
  * previous call left in it: a call overwrites every slot it later reads, so
  * nothing needs clearing, but two calls that overlap on the GPU (different
  * streams without an ordering between them) race on it.  Calls on one stream are

@@ -39,14 +39,83 @@ def ext():
     return _ext
 
 
-def _create(store, rank, size, timeout):
-    return ext().create_backend(store, rank, size, timeout)
+class Options:
+    """Backend options, passed as ``pg_options`` to ``init_process_group`` / ``new_group``
+    (same fields as the FlagCX torch plugin's ``flagcxBackend::Options``,
+    plugin/torch/flagcx/include/backend_flagcx.hpp:104-114 in the FlagCX project).
+
+    enable_tuner   remember every collective's (operation, bytes); ``tune_recorded``
+                   then measures exactly those sizes and stores the winners.
+    tune_group_idx label of this group in the recorded tune-object file.
+    """
+
+    def __init__(self, enable_tuner: bool = False, tune_group_idx: int = 0):
+        self.enable_tuner = bool(enable_tuner)
+        self.tune_group_idx = int(tune_group_idx)
+
+
+def _create(dist_backend_opts, pg_options):
+    o = pg_options if isinstance(pg_options, Options) else Options(
+        enable_tuner=os.environ.get("FLAGCX_TORCH_ENABLE_TUNER", "0") not in ("", "0"))
+    return ext().create_backend(dist_backend_opts.store, dist_backend_opts.group_rank, dist_backend_opts.group_size,
+                                dist_backend_opts.timeout, o.enable_tuner, o.tune_group_idx)
 
 
 def register() -> None:
     if "flagcx" in getattr(dist.Backend, "backend_list", []):
         return
-    dist.Backend.register_backend("flagcx", _create, devices=["cpu", "cuda"])
+    dist.Backend.register_backend("flagcx", _create, extended_api=True, devices=["cpu", "cuda"])
+
+
+def tune_objects(group=None, device=None):
+    """[(operation code, bytes)] of the distinct collectives a group with enable_tuner has run."""
+    group = group or dist.group.WORLD
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return list(ext().tune_objects(group._get_backend(device)))
+
+
+def tune_recorded(group=None, device=None, iters: int = 5, path: str | None = None):
+    """Collective.  Measures every recorded (operation, size) with the library's tuner
+    (all applicable algorithms and CTA counts, max over ranks), keeps the winners in the
+    communicator's table and writes it to `path` or $FLAGCX_TUNE_FILE on rank 0.  Also
+    writes the list of tune objects next to it as ``<path>.pid<pid>`` in the layout the
+    FlagCX plugin uses ({"<group idx>": {"tune_objects": [{"commOp", "nBytes"}]}}).
+    Returns the number of sizes measured."""
+    import json
+    group = group or dist.group.WORLD
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    backend = group._get_backend(device)
+    objs = sorted(ext().tune_objects(backend))
+    _, idx = ext().backend_options(backend)
+    comm = comm_of(group, device)
+    tunable = {capi.OP_ALLREDUCE, capi.OP_ALLGATHER, capi.OP_REDUCESCATTER, capi.OP_ALLTOALL}
+    done = 0
+    for op, nbytes in objs:
+        if op in tunable and nbytes >= 1024:
+            comm.tune(op, capi.BFLOAT16, nbytes, nbytes, iters)
+            done += 1
+    path = path or os.environ.get("FLAGCX_TUNE_FILE")
+    if path and dist.get_rank(group) == 0:
+        comm.tuner_save(path)
+        with open(f"{path}.pid{os.getpid()}", "w") as f:
+            json.dump({str(idx): {"tune_objects": [{"commOp": int(o), "nBytes": int(b)} for o, b in objs]}}, f, indent=2)
+    return done
+
+
+def follow_torch_allocator(comm: capi.Comm, device: int | None = None) -> None:
+    """For a communicator created through ``flagcx_b200.capi`` (not through
+    ``init_process_group``) that is handed torch tensors: before PyTorch's caching
+    allocator returns a segment to the driver (``torch.cuda.empty_cache()``, out-of-memory
+    retries), the peers unmap it.  Process groups of this backend do this by themselves.
+    Call ``unfollow_torch_allocator`` before destroying the communicator."""
+    device = torch.cuda.current_device() if device is None else device
+    ext().follow_allocator(int(comm.h.value), int(device))
+
+
+def unfollow_torch_allocator(comm: capi.Comm) -> None:
+    ext().unfollow_allocator(int(comm.h.value))
 
 
 def comm_of(group=None, device=None) -> capi.Comm:

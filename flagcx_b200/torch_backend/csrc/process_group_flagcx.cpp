@@ -26,6 +26,7 @@
 #include <memory>
 #include <mutex>
 #include <optional>
+#include <set>
 
 #include "flagcx.h"
 #include "flagcx_ext.h"
@@ -61,6 +62,17 @@ flagcxDataType_t toFlagcxType(at::ScalarType t) {
 }
 
 flagcxRedOp_t toFlagcxOp(const c10d::ReduceOp &op, at::ScalarType t) {
+  if (t == at::kBool) {
+    // bool travels as uint8: a sum would wrap at 256 ranks' worth of ones and, worse,
+    // yield values other than 0/1.  Sum is a logical or (max), product a logical and (min).
+    switch (op) {
+      case c10d::ReduceOp::SUM:
+      case c10d::ReduceOp::MAX: return flagcxMax;
+      case c10d::ReduceOp::PRODUCT:
+      case c10d::ReduceOp::MIN: return flagcxMin;
+      default: TORCH_CHECK(false, "flagcx: this reduce op is not defined for bool tensors");
+    }
+  }
   switch (op) {
     case c10d::ReduceOp::SUM: return flagcxSum;
     case c10d::ReduceOp::PRODUCT: return flagcxProd;
@@ -93,16 +105,56 @@ class WorkFlagCX : public c10d::Work {
   c10::intrusive_ptr<c10::ivalue::Future> future_;
 };
 
+// Communicators that must hear about segments the caching allocator hands back to the
+// driver: an allocation that peers have mapped (on-demand export of user buffers) has to
+// be unmapped there before it is freed.  The allocator calls its trace trackers right
+// before cudaFree of a segment, under its own lock; the callback below only talks to the
+// peers' registration threads over a socket and calls nothing of torch.
+std::mutex gLiveMu;
+std::set<std::pair<flagcxComm_t, int>> gLiveComms; // (communicator, CUDA device)
+
+void followAllocator(flagcxComm_t comm, int device) {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    c10::cuda::CUDACachingAllocator::attachAllocatorTraceTracker([](const c10::cuda::CUDACachingAllocator::TraceEntry &te) {
+      if (te.action_ != c10::cuda::CUDACachingAllocator::TraceEntry::SEGMENT_FREE) return;
+      std::lock_guard<std::mutex> g(gLiveMu);
+      for (auto &cd : gLiveComms)
+        if (cd.second == (int)te.device_) flagcxCommForgetUserBuffer(cd.first, (const void *)te.addr_);
+    });
+  });
+  {
+    std::lock_guard<std::mutex> g(gLiveMu);
+    gLiveComms.insert({comm, device});
+  }
+  // frees are now announced to the peers, so any tensor may be exported on first use
+  flagcxCommSetAutoExport(comm, 1);
+}
+void unfollowAllocator(flagcxComm_t comm) {
+  std::lock_guard<std::mutex> g(gLiveMu);
+  for (auto it = gLiveComms.begin(); it != gLiveComms.end();)
+    it = it->first == comm ? gLiveComms.erase(it) : std::next(it);
+}
+
+// Options of the backend, same two fields as the FlagCX torch plugin
+// (plugin/torch/flagcx/include/backend_flagcx.hpp:104-114 in the FlagCX project).  With
+// enableTuner every collective's (operation, bytes) is remembered as a "tune object";
+// flagcx_b200.torch_backend.tune_recorded() later measures exactly those sizes.
+struct FlagcxOptions {
+  bool enableTuner = false;
+  int tuneGroupIdx = 0;
+};
+
 class ProcessGroupFlagCX : public c10d::Backend {
  public:
-  ProcessGroupFlagCX(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size)
-      : c10d::Backend(rank, size), store_(store) {
+  ProcessGroupFlagCX(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size, FlagcxOptions options = {})
+      : c10d::Backend(rank, size), store_(store), options_(options) {
     const char *cur = std::getenv("FLAGCX_TORCH_USE_CURRENT_STREAM");
     useCurrentStream_ = cur && std::atoi(cur) != 0;
   }
 
   ~ProcessGroupFlagCX() override {
-    if (comm_) flagcxCommDestroy(comm_);
+    if (comm_) { unfollowAllocator(comm_); flagcxCommDestroy(comm_); }
   }
 
   const std::string getBackendName() const override { return "flagcx"; }
@@ -110,16 +162,22 @@ class ProcessGroupFlagCX : public c10d::Backend {
   void setSequenceNumberForGroup() override {}
   uint64_t getSequenceNumberForGroup() override { return seq_; }
   void abort() override {
-    if (comm_) { flagcxCommAbort(comm_); comm_ = nullptr; }
+    if (comm_) { unfollowAllocator(comm_); flagcxCommAbort(comm_); comm_ = nullptr; }
   }
   void shutdown() override {
-    if (comm_) { flagcxCommDestroy(comm_); comm_ = nullptr; }
+    if (comm_) { unfollowAllocator(comm_); flagcxCommDestroy(comm_); comm_ = nullptr; }
   }
   void eagerConnectSingleDevice(at::Device device) override { ensureComm(device); }
 
   flagcxComm_t comm(const at::Device &device) {
     ensureComm(device);
     return comm_;
+  }
+  const FlagcxOptions &options() const { return options_; }
+  // (operation, bytes) of every distinct collective seen so far (enableTuner only)
+  std::vector<std::pair<int, uint64_t>> tuneObjects() {
+    std::lock_guard<std::mutex> g(mu_);
+    return std::vector<std::pair<int, uint64_t>>(tuneObjects_.begin(), tuneObjects_.end());
   }
 
   // ---- coalescing --------------------------------------------------------------
@@ -439,7 +497,14 @@ class ProcessGroupFlagCX : public c10d::Backend {
   void ensureComm(const at::Device &dev) {
     std::lock_guard<std::mutex> g(mu_);
     if (dev.is_cuda()) lastDevice_ = dev;
-    if (comm_) return;
+    if (comm_) {
+      // one communicator, bound to one GPU at creation: a tensor on another GPU of this
+      // process cannot use it
+      TORCH_CHECK(!dev.is_cuda() || commDevice_ < 0 || dev.index() == commDevice_,
+                  "flagcx: this process group was initialised on cuda:", commDevice_, " but got a tensor on cuda:",
+                  (int)dev.index(), "; call torch.cuda.set_device() before the first collective");
+      return;
+    }
     std::optional<c10::cuda::CUDAGuard> guard;
     if (dev.is_cuda()) guard.emplace(dev);
     // id exchange through the c10d store; one key per communicator instance
@@ -457,6 +522,29 @@ class ProcessGroupFlagCX : public c10d::Backend {
       std::memcpy(&id, bytes.data(), sizeof id);
     }
     FCX_TORCH_CHECK(flagcxCommInitRank(&comm_, getSize(), &id, getRank()), nullptr);
+    // the GPU the communicator bound itself to (the current device if the first tensor was
+    // a CPU tensor); -1 on hosts without one
+    int devNo = -1;
+    if (flagcxCommGetDeviceNumber(comm_, &devNo) == flagcxSuccess) commDevice_ = devNo;
+    if (commDevice_ >= 0) followAllocator(comm_, commDevice_);
+  }
+
+  static int commOpOf(c10d::OpType op) {
+    switch (op) {
+      case c10d::OpType::ALLREDUCE:
+      case c10d::OpType::ALLREDUCE_COALESCED: return flagcxCommOpAllReduce;
+      case c10d::OpType::BROADCAST: return flagcxCommOpBroadcast;
+      case c10d::OpType::REDUCE: return flagcxCommOpReduce;
+      case c10d::OpType::ALLGATHER:
+      case c10d::OpType::_ALLGATHER_BASE: return flagcxCommOpAllGather;
+      case c10d::OpType::REDUCE_SCATTER:
+      case c10d::OpType::_REDUCE_SCATTER_BASE: return flagcxCommOpReduceScatter;
+      case c10d::OpType::ALLTOALL_BASE:
+      case c10d::OpType::ALLTOALL: return flagcxCommOpAlltoAll;
+      case c10d::OpType::GATHER: return flagcxCommOpGather;
+      case c10d::OpType::SCATTER: return flagcxCommOpScatter;
+      default: return -1;
+    }
   }
 
   template <typename Fn>
@@ -464,6 +552,14 @@ class ProcessGroupFlagCX : public c10d::Backend {
                                      const std::vector<at::Tensor> &outputs, Fn fn,
                                      std::function<void()> post = {}, bool p2p = false) {
     ++seq_;
+    if (options_.enableTuner && commOpOf(op) >= 0) {
+      // the size the library's tuner keys on: the larger side of the operation
+      uint64_t in = 0, out = 0;
+      for (auto &t : inputs) in += (uint64_t)t.nbytes();
+      for (auto &t : outputs) out += (uint64_t)t.nbytes();
+      std::lock_guard<std::mutex> g(mu_);
+      tuneObjects_.insert({commOpOf(op), std::max(in, out)});
+    }
     const at::Tensor &probe = !inputs.empty() ? inputs[0] : outputs[0];
     at::Device dev = probe.device();
     ensureComm(dev);
@@ -522,12 +618,27 @@ class ProcessGroupFlagCX : public c10d::Backend {
   bool coalescing_ = false, groupOpen_ = false, useCurrentStream_ = false;
   uint64_t seq_ = 0;
   int groupCounter_ = 0;
+  int commDevice_ = -1;
+  FlagcxOptions options_;
+  std::set<std::pair<int, uint64_t>> tuneObjects_;
   std::mutex mu_;
 };
 
 c10::intrusive_ptr<c10d::Backend> createBackend(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size,
-                                                const std::chrono::duration<float> &) {
-  return c10::make_intrusive<ProcessGroupFlagCX>(store, rank, size);
+                                                const std::chrono::duration<float> &, bool enableTuner,
+                                                int tuneGroupIdx) {
+  return c10::make_intrusive<ProcessGroupFlagCX>(store, rank, size, FlagcxOptions{enableTuner, tuneGroupIdx});
+}
+
+std::vector<std::pair<int, uint64_t>> tuneObjects(const c10::intrusive_ptr<c10d::Backend> &backend) {
+  auto *pg = dynamic_cast<ProcessGroupFlagCX *>(backend.get());
+  TORCH_CHECK(pg, "not a flagcx backend");
+  return pg->tuneObjects();
+}
+std::pair<bool, int> backendOptions(const c10::intrusive_ptr<c10d::Backend> &backend) {
+  auto *pg = dynamic_cast<ProcessGroupFlagCX *>(backend.get());
+  TORCH_CHECK(pg, "not a flagcx backend");
+  return {pg->options().enableTuner, pg->options().tuneGroupIdx};
 }
 
 // Raw flagcxComm_t of a backend (as an integer) so Python can drive the C API --
@@ -542,6 +653,14 @@ uintptr_t commHandle(const c10::intrusive_ptr<c10d::Backend> &backend, const at:
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "torch.distributed backend 'flagcx' (B200-native collectives)";
-  m.def("create_backend", &createBackend, py::arg("store"), py::arg("rank"), py::arg("size"), py::arg("timeout"));
+  m.def("create_backend", &createBackend, py::arg("store"), py::arg("rank"), py::arg("size"), py::arg("timeout"),
+        py::arg("enable_tuner") = false, py::arg("tune_group_idx") = 0);
+  m.def("tune_objects", &tuneObjects, py::arg("backend"));
+  m.def("follow_allocator", [](uintptr_t comm, int device) { followAllocator((flagcxComm_t)comm, device); },
+        py::arg("comm_handle"), py::arg("device"),
+        "Have a communicator created outside torch.distributed unmap, on its peers, every segment the caching "
+        "allocator is about to free.");
+  m.def("unfollow_allocator", [](uintptr_t comm) { unfollowAllocator((flagcxComm_t)comm); }, py::arg("comm_handle"));
+  m.def("backend_options", &backendOptions, py::arg("backend"));
   m.def("comm_handle", &commHandle, py::arg("backend"), py::arg("device"));
 }

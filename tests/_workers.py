@@ -339,6 +339,8 @@ def gpu_user_buffers_under_skew(rank, n, uid, rounds):
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
     assert comm.device_path, "expected the NVLink device path"
     exporting = bool(comm.user_buffer_stats().enabled)
+    import flagcx_b200.torch_backend as tb
+    tb.follow_torch_allocator(comm)  # segments freed by empty_cache() below are unmapped at the peers first
     # different allocation histories: segments and offsets differ between the ranks
     ballast = [torch.empty((rank + 1) * (3 << 20) + 4096 * i, dtype=torch.uint8, device="cuda") for i in range(rank + 2)]
     small_n, big_n, per = 1024, (6 << 20) + 16 * n, (1 << 20)
@@ -380,9 +382,106 @@ def gpu_user_buffers_under_skew(rank, n, uid, rounds):
     assert comm.async_error() == 0, comm.last_error()
     comm.barrier()
     del ballast
+    tb.unfollow_torch_allocator(comm)
     comm.destroy()
     return {"bad": bad, "exporting": exporting, "exports": int(st.exports), "hits": int(st.hits),
             "refused": int(st.refused), "stale": int(st.stale)}
+
+
+def gpu_nvls_collectives(rank, n, uid, count):
+    """The multimem (NVLink SHARP) kernels on registered windows: all-reduce one- and
+    two-shot, reduce-scatter, all-gather, against fp64 sums of the same seeded inputs.
+    Every rank stays alive until all of them have unbound their memory."""
+    import torch
+    from flagcx_b200.utils.symm import SymmetricBuffer
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    if not comm.has_multicast:
+        comm.destroy()
+        return {"skipped": 1.0}
+    worst, bufs = {}, []
+
+    def alloc(numel, tdt):
+        b = SymmetricBuffer(comm, max(numel * torch.empty((), dtype=tdt).element_size(), 1 << 21))
+        bufs.append(b)
+        return b.view(tdt, numel)
+
+    try:
+        for dt, tdt, tol in ((capi.FLOAT, torch.float32, 1e-6), (capi.BFLOAT16, torch.bfloat16, 2 ** -7 * n)):
+            cpu = [_torch_seeded(r, count * n, tdt) for r in range(n)]
+            ref = torch.stack([c.to(torch.float64) for c in cpu]).sum(0)
+            x = alloc(count * n, tdt)
+            x.copy_(cpu[rank])
+            for algo in (capi.ALGO_NVLS_ONESHOT, capi.ALGO_NVLS_TWOSHOT):
+                out = alloc(count * n, tdt)
+                out.zero_()
+                comm.all_reduce_fused(x, out, count * n, dt, capi.SUM, algo=algo)
+                torch.cuda.synchronize()
+                if comm.stats(capi.OP_ALLREDUCE).lastAlgo != algo:
+                    worst[f"allreduce{algo}_{dt}_fell_back"] = 2.0  # the multimem kernel did not run
+                err = ((out.cpu().to(torch.float64) - ref).abs() / ref.abs().clamp(min=1)).max().item()
+                worst[f"allreduce{algo}_{dt}"] = err / tol
+            rs = alloc(count, tdt)
+            comm.reduce_scatter_fused(x, rs, count, dt, capi.SUM, algo=capi.ALGO_NVLS)
+            torch.cuda.synchronize()
+            if comm.stats(capi.OP_REDUCESCATTER).lastAlgo != capi.ALGO_NVLS:
+                worst[f"reducescatter_{dt}_fell_back"] = 2.0
+            sl = ref[rank * count:(rank + 1) * count]
+            worst[f"reducescatter_{dt}"] = ((rs.cpu().to(torch.float64) - sl).abs() / sl.abs().clamp(min=1)).max().item() / tol
+            ag = alloc(count * n, tdt)
+            ag.zero_()
+            comm.all_gather(x[:count], ag, count, dt, algo=capi.ALGO_NVLS)
+            torch.cuda.synchronize()
+            if comm.stats(capi.OP_ALLGATHER).lastAlgo != capi.ALGO_NVLS:
+                worst[f"allgather_{dt}_fell_back"] = 2.0
+            worst[f"allgather_{dt}"] = float(not torch.equal(ag.cpu(), torch.cat([c[:count] for c in cpu])))
+        if comm.async_error() != 0:
+            worst["device_error"] = 2.0
+    finally:
+        # nobody leaves while a peer's memory is still bound to the multicast object
+        for b in bufs:
+            b.free()
+        comm.destroy()
+    return worst
+
+
+def gpu_two_level(rank, n, uid, per_node):
+    """A machine split into nodes of `per_node` ranks (FLAGCX_HOSTID per rank, set by the
+    test): all-reduce and all-gather take the two-level route (NVLink kernels inside a
+    node, host network between), everything else the flat host route."""
+    import torch
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    assert not comm.device_path, "the split must take the communicator off the single-domain device path"
+    worst = {}
+    for dt, tdt, tol in ((capi.FLOAT, torch.float32, 1e-6), (capi.BFLOAT16, torch.bfloat16, 2 ** -7 * n)):
+        for count in (3, 1000, 70003, (1 << 20) + 8):
+            cpu = [_torch_seeded(r, count, tdt) for r in range(n)]
+            ref = torch.stack([c.to(torch.float64) for c in cpu]).sum(0)
+            x = cpu[rank].cuda()
+            out = torch.empty_like(x)
+            comm.all_reduce(x, out, count, dt, capi.SUM)
+            torch.cuda.synchronize()
+            err = ((out.cpu().to(torch.float64) - ref).abs() / ref.abs().clamp(min=1)).max().item()
+            worst[f"allreduce_{dt}_{count}"] = err / tol
+            comm.all_reduce(x, x, count, dt, capi.AVG)  # in place
+            torch.cuda.synchronize()
+            err = ((x.cpu().to(torch.float64) - ref / n).abs() / (ref / n).abs().clamp(min=1)).max().item()
+            worst[f"allreduce_avg_{dt}_{count}"] = err / tol
+            ag = torch.zeros(count * n, dtype=tdt, device="cuda")
+            comm.all_gather(cpu[rank].cuda(), ag, count, dt)
+            torch.cuda.synchronize()
+            worst[f"allgather_{dt}_{count}"] = float(not torch.equal(ag.cpu(), torch.cat(cpu)))
+    # an operation without a two-level route: flat host path
+    cnt = 4099
+    cpu = [_torch_seeded(r, cnt * n, torch.float32) for r in range(n)]
+    rs = torch.empty(cnt, device="cuda")
+    comm.reduce_scatter(cpu[rank].cuda(), rs, cnt, capi.FLOAT, capi.SUM)
+    torch.cuda.synchronize()
+    ref = torch.stack(cpu).to(torch.float64).sum(0)[rank * cnt:(rank + 1) * cnt]
+    worst["reducescatter_flat"] = ((rs.cpu().to(torch.float64) - ref).abs().max().item()) / 1e-5
+    comm.destroy()
+    return worst
 
 
 def gpu_peer_never_launches(rank, n, uid):
@@ -480,6 +579,37 @@ def torch_backend_ops(rank, n, uid_unused, port, use_cuda):
         dist.barrier()
         if use_cuda:
             torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+    return "ok"
+
+
+def torch_backend_options(rank, n, uid_unused, port):
+    """pg_options of the backend: with enable_tuner every collective's (operation, bytes)
+    is recorded; bool tensors reduce as logical or / and."""
+    import torch
+    import torch.distributed as dist
+    import flagcx_b200.torch_backend as tb
+    dist.init_process_group("flagcx", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n,
+                            pg_options=tb.Options(enable_tuner=True, tune_group_idx=3))
+    try:
+        dev = torch.device("cpu")
+        t = torch.ones(1000)
+        dist.all_reduce(t)
+        dist.all_reduce(torch.ones(50))
+        dist.all_reduce(torch.ones(1000))  # same size again: one tune object
+        flat = torch.empty(16 * n)
+        dist.all_gather_into_tensor(flat, torch.ones(16))
+        objs = tb.tune_objects(dist.group.WORLD, dev)
+        assert (capi.OP_ALLREDUCE, 4000) in objs and (capi.OP_ALLREDUCE, 200) in objs, objs
+        assert (capi.OP_ALLGATHER, 64 * n) in objs and len(objs) == 3, objs
+        b = torch.tensor([rank == 0, False, True])
+        dist.all_reduce(b)  # sum of bools: logical or
+        assert b.tolist() == [True, False, True], b
+        b = torch.tensor([rank == 0, False, True])
+        dist.all_reduce(b, op=dist.ReduceOp.PRODUCT)  # logical and
+        assert b.tolist() == [False, False, True], b
+        dist.barrier()
     finally:
         dist.destroy_process_group()
     return "ok"

@@ -21,6 +21,11 @@ def test_process_group_ops_cpu(n):
     assert all(v == "ok" for v in res.values())
 
 
+def test_backend_options_record_tune_objects_and_bool_reductions():
+    res = run_ranks(2, "torch_backend_options", free_port(), timeout=300)
+    assert all(v == "ok" for v in res.values())
+
+
 def test_ddp_loss_parity_with_gloo():
     ours = run_ranks(2, "torch_ddp_parity", free_port(), "flagcx", False, timeout=300)
     gloo = run_ranks(2, "torch_ddp_parity", free_port(), "gloo", False, timeout=300)

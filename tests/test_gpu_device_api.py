@@ -143,6 +143,19 @@ def test_reset_signals_and_counters(world):
     assert bool((res[:, 0] == 1).all())
 
 
+def test_c_linkage_wrappers(world):
+    """flagcx_device_c.cuh: put with remote signal and local counter, get, putValue with
+    signal, shadows, flush and the split barrier, called by their extern "C" names."""
+    for _ in range(2):  # the kernel resets its signals and counters, so it can run again
+        res = world.run(10)
+        assert bool((res[:, 0] == 1).all()), res[:, 0]
+    half = world.n_words // 2
+    for r in range(world.n):
+        prev = (r - 1) % world.n
+        assert torch.equal(world.bufs[r][half:2 * half - 1].cpu(), (torch.arange(half) + prev * 100000)[:half - 1])
+        assert int(world.bufs[r][world.n_words - 1]) == 0xabc000 + prev
+
+
 def test_unsatisfied_wait_returns_false_and_reports():
     w = World(2, timeout_ms=150)
     try:

@@ -138,3 +138,51 @@ def test_torch_backend_ops_on_gpus():
     n = 2
     res = run_ranks(n, "torch_backend_ops", free_port(), True, timeout=300)
     assert all(v == "ok" for v in res.values())
+
+
+def test_optimizer_under_backward_gives_the_same_model():
+    """AdamW of a unit queued right behind that unit's gradients (on its own stream, under
+    the rest of the backward pass) against AdamW after the whole backward pass: same
+    losses, same parameters."""
+    from flagcx_b200 import ops
+    from flagcx_b200.models.llama import LlamaConfig, build_units
+    from flagcx_b200.parallel.fsdp import ShardedModel
+    cfg = LlamaConfig.tiny()
+    ops.assume_unit_loss_grad = True
+    g = torch.Generator().manual_seed(3)
+    batches = [torch.randint(0, cfg.vocab, (129,), generator=g).cuda() for _ in range(4)]
+    runs = []
+    for overlap in (False, True):
+        m = ShardedModel(build_units(cfg), None, 0, 1, torch.device("cuda", 0), overlap_optimizer=overlap)
+        losses = [float(m.train_step(b[:-1], b[1:])) for b in batches]
+        torch.cuda.synchronize()
+        runs.append((losses, [s.clone() for s in m.shard]))
+        m.close()
+    (la, pa), (lb, pb) = runs
+    assert max(abs(x - y) for x, y in zip(la, lb)) < 2e-2, (la, lb)
+    for x, y in zip(pa, pb):
+        assert (x.float() - y.float()).abs().max().item() < 2e-2
+
+
+def test_checkpoint_round_trip_resumes_with_the_same_loss():
+    """state_dict -> load_state_dict into a fresh engine: the next step's loss is the one
+    the original engine computes (parameters, both AdamW moments and the step counter)."""
+    from flagcx_b200 import ops
+    from flagcx_b200.models.llama import LlamaConfig, build_units
+    from flagcx_b200.parallel.fsdp import ShardedModel
+    cfg = LlamaConfig.tiny()
+    ops.assume_unit_loss_grad = True
+    g = torch.Generator().manual_seed(11)
+    batches = [torch.randint(0, cfg.vocab, (129,), generator=g).cuda() for _ in range(4)]
+    a = ShardedModel(build_units(cfg), None, 0, 1, torch.device("cuda", 0), lr=1e-3)
+    for b in batches[:2]:
+        a.train_step(b[:-1], b[1:])
+    sd = a.state_dict()
+    want = [float(a.train_step(b[:-1], b[1:])) for b in batches[2:]]
+    fresh = ShardedModel(build_units(cfg), None, 0, 1, torch.device("cuda", 0), lr=1e-3, seed=999)  # other weights
+    fresh.load_state_dict(sd)
+    got = [float(fresh.train_step(b[:-1], b[1:])) for b in batches[2:]]
+    assert fresh.step_count == a.step_count
+    assert max(abs(x - y) for x, y in zip(want, got)) < 2e-2, (want, got)
+    a.close()
+    fresh.close()

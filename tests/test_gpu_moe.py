@@ -9,6 +9,15 @@ from flagcx_b200.parallel.moe import MoeDispatcher, route
 pytestmark = pytest.mark.gpu
 
 
+def _sorted_rows(rows: torch.Tensor) -> torch.Tensor:
+    """Rows in lexicographic order of their exact bit patterns, so that two tensors hold the
+    same multiset of rows exactly when the results are equal element for element."""
+    bits = rows.contiguous().view(torch.int16).to(torch.int64).cpu()
+    order = list(range(bits.shape[0]))
+    order.sort(key=lambda i: bits[i].tolist())
+    return bits[order]
+
+
 @pytest.mark.parametrize("n,T,H,E,K", [(2, 33, 128, 8, 2), (4, 64, 256, 16, 4), (8, 96, 512, 64, 8)])
 def test_dispatch_groups_rows_by_expert_and_combine_weights_them(n, T, H, E, K):
     comms = capi.Comm.emu_world(n, 0)
@@ -34,8 +43,9 @@ def test_dispatch_groups_rows_by_expert_and_combine_weights_them(n, T, H, E, K):
                     sel = (routed[s][0] == e).any(dim=1).cpu()
                     rows = xs[s].cpu()[sel]
                     got = moes[d].recv_rows[offs[le] + len(want_rows): offs[le] + len(want_rows) + rows.shape[0]].cpu()
-                    # order inside one (source, expert) group is arbitrary: compare as sorted sets of rows
-                    assert torch.equal(torch.sort(got.float().sum(1)).values, torch.sort(rows.float().sum(1)).values), (d, e, s)
+                    # order inside one (source, expert) group is arbitrary: compare whole rows as
+                    # multisets (rows sorted lexicographically, then element for element)
+                    assert torch.equal(_sorted_rows(got), _sorted_rows(rows)), (d, e, s)
                     want_rows.extend([None] * rows.shape[0])
                 assert offs[le + 1] - offs[le] == len(want_rows)
             # the "expert": scale every row of expert e by (e + 1)

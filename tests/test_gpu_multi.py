@@ -48,6 +48,31 @@ def test_plain_tensors_with_a_straggler(export):
 
 
 @needs2
+def test_nvls_multimem_kernels():
+    """FLAGCX_NVLS_ENABLE=1: the switch reduces (multimem.ld_reduce) and replicates
+    (multimem.st).  Skipped where the GPUs expose no multicast."""
+    n = 8 if ngpus() >= 8 else 4 if ngpus() >= 4 else 2
+    res = run_ranks(n, "gpu_nvls_collectives", 1 << 16, env={"FLAGCX_NVLS_ENABLE": "1"}, timeout=300)
+    if all("skipped" in v for v in res.values()):
+        pytest.skip("no NVLink multicast on this machine")
+    for rank, worst in res.items():
+        bad = {k: v for k, v in worst.items() if v > 1.0}
+        assert not bad, (rank, bad)
+
+
+@needs2
+def test_two_level_route_when_one_machine_poses_as_several_nodes():
+    """FLAGCX_HOSTID splits the machine: 2 nodes x 2 GPUs where there are four, else 2 x 1."""
+    per_node = 2 if ngpus() >= 4 else 1
+    n = 2 * per_node
+    env = {r: {"FLAGCX_HOSTID": f"node{r // per_node}"} for r in range(n)}
+    res = run_ranks(n, "gpu_two_level", per_node, per_rank_env=env, timeout=300)
+    for rank, worst in res.items():
+        bad = {k: v for k, v in worst.items() if v > 1.0}
+        assert not bad, (rank, bad)
+
+
+@needs2
 def test_missing_peer_becomes_an_error_code():
     n = 2
     env = {"NCCL_NVLS_ENABLE": "0", "FLAGCX_NVLS_ENABLE": "0"}
