@@ -132,6 +132,8 @@ def run_ours(args) -> dict:
         losses.append(trainer.step(host_batches[i]))
     sync_all()
 
+    if args.trace_comm and comm is not None:
+        comm.trace_enable(8192)  # every collective of the timed steps: operation, bytes, CTAs, device time
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -147,6 +149,10 @@ def run_ours(args) -> dict:
     e1.record()
     sync_all()
     dev_ms = max_ranks(e0.elapsed_time(e1))
+    if args.trace_comm and comm is not None:
+        if rank == 0:
+            comm.trace_dump(args.trace_comm)
+        comm.trace_enable(0)
     launches = ops.launch_count + model.comm_launches - launches0
     losses.append(float(loss))
 
@@ -203,6 +209,8 @@ def main():
                          "ProcessGroup / over NCCL")
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--trace-comm", default="", help="write rank 0's per-collective trace of the timed steps (JSON) here; "
+                                                     "summarise it with bench/trace_summary.py")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

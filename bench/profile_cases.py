@@ -7,8 +7,14 @@ figures matter).  Each case also prints its CUDA-event time.
     python bench/profile_cases.py --case allreduce       # 8 emulated ranks, two-shot, 32 MiB bf16 each
     python bench/profile_cases.py --case reducescatter   # 8 emulated ranks, 8 x 8 MiB bf16 each
     python bench/profile_cases.py --case allgather       # 8 emulated ranks, push
+    python bench/profile_cases.py --case alltoall        # 8 emulated ranks, 8 x 4 MiB blocks each (copyKernelEmu)
+    python bench/profile_cases.py --case sendrecv        # 8 emulated ranks, ring of 32 MiB messages (p2pKernelEmu)
+    python bench/profile_cases.py --case ll              # 8 emulated ranks, 16 KiB all-reduce, barrier-free (llKernelEmu)
+    python bench/profile_cases.py --case ring            # 8 emulated ranks, ring all-reduce of 32 MiB
+    python bench/profile_cases.py --case allreduce_cast  # 8 emulated ranks, bf16 in / fp32 out two-shot, 32 MiB
+    python bench/profile_cases.py --case putsignal       # 2 emulated ranks, flagcxPutSignal of 64 MiB
     python bench/profile_cases.py --case moe             # 8 emulated ranks, 512 tokens x 7168, top-8 of 256
-    python bench/profile_cases.py --case model_kernels   # RMSNorm / SwiGLU / cross-entropy / AdamW
+    python bench/profile_cases.py --case model_kernels   # RMSNorm / SwiGLU / cross-entropy / AdamW / RoPE
 
 The multi-rank cases run as an emulated world: all ranks in one cooperative launch
 on one GPU, so "peer" traffic is local HBM traffic there -- they show instruction mix,
@@ -76,6 +82,54 @@ def main():
         print(f"{args.case} emulated x{n}: {us:.1f} us for {moved >> 20} MiB of payload in the world")
         assert comms[0].async_error() == 0
         capi.Comm.emu_world_destroy(comms)
+    elif args.case in ("alltoall", "sendrecv", "ll", "ring", "allreduce_cast"):
+        n = 8
+        comms = capi.Comm.emu_world(n, 0)
+        if args.case == "alltoall":
+            per = (4 << 20) // 2
+            xs = [torch.randn(per * n, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            outs = [torch.empty(per * n, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+            run = lambda: [comms[r].all_to_all(xs[r], outs[r], per, capi.BFLOAT16) for r in range(n)]
+            moved = per * n * 2 * n
+        elif args.case == "sendrecv":
+            cnt = (32 << 20) // 2
+            xs = [torch.randn(cnt, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            outs = [torch.empty(cnt, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+
+            def run():
+                for r in range(n):
+                    comms[r].group_start()
+                    comms[r].send(xs[r], cnt, capi.BFLOAT16, (r + 1) % n)
+                    comms[r].recv(outs[r], cnt, capi.BFLOAT16, (r - 1) % n)
+                    comms[r].group_end()
+            moved = cnt * 2 * n
+        else:
+            cnt = (16 << 10) // 2 if args.case == "ll" else (32 << 20) // 2
+            xs = [torch.randn(cnt, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            cast = args.case == "allreduce_cast"
+            outs = [torch.empty(cnt, dtype=torch.float32 if cast else torch.bfloat16, device="cuda") for _ in range(n)]
+            algo = {"ll": capi.ALGO_LL, "ring": capi.ALGO_RING, "allreduce_cast": capi.ALGO_TWOSHOT}[args.case]
+            run = lambda: [comms[r].all_reduce_fused(xs[r], outs[r], cnt, capi.BFLOAT16, capi.SUM, algo=algo,
+                                                     scale=1.0 / n if cast else 1.0,
+                                                     out_dtype=capi.FLOAT if cast else capi.NUM_TYPES) for r in range(n)]
+            moved = cnt * 2 * n
+        us = timed(run)
+        print(f"{args.case} emulated x{n}: {us:.1f} us for {moved / (1 << 20):.2f} MiB of payload in the world")
+        assert comms[0].async_error() == 0, comms[0].last_error()
+        capi.Comm.emu_world_destroy(comms)
+    elif args.case == "putsignal":
+        n, cnt = 2, (64 << 20) // 2
+        comms = capi.Comm.emu_world(n, 0)
+        bufs = [torch.zeros(cnt, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+        wins = [comms[r].window_register(bufs[r], cnt * 2) for r in range(n)]
+        src = torch.randn(cnt, device="cuda").to(torch.bfloat16)
+
+        def run():  # rank 0 puts into rank 1's window and raises its signal
+            capi.check(capi.lib().flagcxPutSignal(capi._ptr(src), capi.C.c_size_t(cnt), capi.BFLOAT16, 1, wins[0],
+                                                  capi.C.c_size_t(0), 0, comms[0].h, None), "flagcxPutSignal", comms[0].h)
+        us = timed(run)
+        print(f"putsignal 64 MiB: {us:.1f} us, {cnt * 2 * 2 / us / 1e3:.0f} GB/s (read + write, one GPU)")
+        capi.Comm.emu_world_destroy(comms)
     elif args.case == "moe":
         from flagcx_b200.parallel.moe import MoeDispatcher, route
         n, T, H, E, K = 8, 512, 7168, 256, 8
@@ -125,6 +179,9 @@ def main():
         v = torch.zeros_like(p)
         us = timed(lambda: ops.ext().adamw_flat_(p, g, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1))
         print(f"adamw {n} params: {us:.1f} us, {7 * n * 2 / us / 1e3:.0f} GB/s (4 reads + 3 writes of bf16)")
+        q = torch.randn(T, 32, 128, device="cuda").to(torch.bfloat16)
+        us = timed(lambda: ops.ext().rope_inplace(q, None, 500000.0, False))
+        print(f"rope {T}x32x128 in place: {us:.1f} us, {2 * q.numel() * 2 / us / 1e3:.0f} GB/s")
     else:
         raise SystemExit(f"unknown case {args.case}")
 

@@ -750,6 +750,17 @@ flagcxResult_t flagcxWaitSignal(int nDesc, const flagcxWaitSignalDesc_t *descs, 
 // ---------------------------------------------------------------------------
 // extensions
 // ---------------------------------------------------------------------------
+// Device collective of the extension entry points, with the same trace record and NVTX range
+// that the FlagCX-compatible entry points get.
+static flagcxResult_t tracedDeviceCollective(flagcxComm *c, const DeviceCollRequest &rq, size_t bytes, flagcxStream_t stream) {
+  nvtxPush(commOpName(rq.op));
+  const int slot = c->trace.begin(c, rq.op, bytes, 0, rawStream(stream));
+  flagcxResult_t r = deviceCollective(c, rq, rawStream(stream));
+  c->trace.end(c, slot, rawStream(stream));
+  nvtxPop();
+  return r;
+}
+
 flagcxResult_t flagcxAllReduceFused(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
                                     flagcxRedOp_t op, const flagcxFusedOpts_t *opts, flagcxComm_t comm,
                                     flagcxStream_t stream) {
@@ -764,7 +775,7 @@ flagcxResult_t flagcxAllReduceFused(const void *sendbuff, void *recvbuff, size_t
     rq.algo = opts->algo;
     rq.nCtas = opts->nCtas > 0 ? opts->nCtas : -1;
   }
-  return deviceCollective(comm, rq, rawStream(stream));
+  return tracedDeviceCollective(comm, rq, count * getFlagcxDataTypeSize(datatype), stream);
 }
 
 flagcxResult_t flagcxReduceScatterFused(const void *sendbuff, void *recvbuff, size_t recvcount,
@@ -781,7 +792,7 @@ flagcxResult_t flagcxReduceScatterFused(const void *sendbuff, void *recvbuff, si
     rq.algo = opts->algo;
     rq.nCtas = opts->nCtas > 0 ? opts->nCtas : -1;
   }
-  return deviceCollective(comm, rq, rawStream(stream));
+  return tracedDeviceCollective(comm, rq, recvcount * getFlagcxDataTypeSize(datatype) * comm->nranks, stream);
 }
 
 flagcxResult_t flagcxAllGatherEx(const void *sendbuff, void *recvbuff, size_t sendcount, flagcxDataType_t datatype,
@@ -792,7 +803,7 @@ flagcxResult_t flagcxAllGatherEx(const void *sendbuff, void *recvbuff, size_t se
   DeviceCollRequest rq{flagcxCommOpAllGather, sendbuff, recvbuff, sendcount, datatype, flagcxSum, 0};
   rq.algo = algo;
   rq.nCtas = nCtas > 0 ? nCtas : -1;
-  return deviceCollective(comm, rq, rawStream(stream));
+  return tracedDeviceCollective(comm, rq, sendcount * getFlagcxDataTypeSize(datatype) * comm->nranks, stream);
 }
 
 flagcxResult_t flagcxTunerTune(flagcxComm_t comm, flagcxCommOp_t op, flagcxDataType_t dtype, size_t minBytes,

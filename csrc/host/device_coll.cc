@@ -224,6 +224,15 @@ int bulkReduceFor(flagcxComm *c, const CollArgs &a) {
   return (bits & 15) ? 0 : 1;
 }
 
+// Extents of the regions behind in[] / out[] for the bounds-checking kernel build.  The
+// regions of a launch are what the operation's definition says they are; a test can make
+// the host understate them (FLAGCX_BOUNDS_TEST_SHRINK bytes) to see a violation reported.
+void setExtents(CollArgs &a, size_t inBytes, size_t outBytes) {
+  static const int64_t shrink = readParam("BOUNDS_TEST_SHRINK", 0);
+  a.inBytes = inBytes > (size_t)shrink ? inBytes - (size_t)shrink : inBytes;
+  a.outBytes = outBytes > (size_t)shrink ? outBytes - (size_t)shrink : outBytes;
+}
+
 flagcxResult_t launch(flagcxComm *c, int family, const CollArgs &a0, int nCtas, cudaStream_t stream) {
   nCtas = std::max(1, std::min(nCtas, FLAGCX_COLL_BARRIER_SLOTS));
   CollArgs a = a0;
@@ -368,6 +377,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       setIn(c, a, BufView(), rq.send);
       setOut(c, a, BufView(), rq.recv);
       note(c, flagcxCommOpAllReduce, count * es, FLAGCX_ALGO_LL, 0);
+      setExtents(a, count * es, count * es);
       return launchLl(c, a, count * es, stream);
     }
   }
@@ -399,6 +409,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
     const bool direct = nvlsAlgo ? inMc : inVis;
     if (direct) {
       a.count = count;
+      setExtents(a, count * es, count * oes);
       applyIn(c, a, uin);
       applyOutLocal(c, a, uout);
       FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
@@ -434,6 +445,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       a.count = cnt;
       a.xchg = 0;
       setRing(c, a, es, 2 * (n - 1));
+      setExtents(a, cnt * es, cnt * oes);
       setIn(c, a, BufView(), uin.local, off * es); // only this rank reads its input
       applyOut(c, a, uout, off * oes);
       FCXCHECK(launch(c, kFamReduce, a, nCtas, stream));
@@ -453,6 +465,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
       const size_t cnt = std::min(perLaunch, count - off);
       a.count = cnt;
       a.xchg = 0;
+      setExtents(a, cnt * es, cnt * oes);
       applyIn(c, a, uin, off * es);
       applyOutLocal(c, a, uout, off * oes);
       a.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
@@ -467,6 +480,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   const bool inDirect = nvlsAlgo ? inMc : inVis, outDirect = nvlsAlgo ? outMc : outVis;
   if (inDirect && outDirect) {
     a.count = count;
+    setExtents(a, count * es, count * oes);
     applyIn(c, a, uin);
     applyOut(c, a, uout);
     FCXCHECK(launch(c, nvlsAlgo ? kFamNvls : kFamReduce, a, nCtas, stream));
@@ -513,6 +527,19 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   initArgs(c, a, kReduceScatter, rq.dtype);
   FCXCHECK(setReduceEpilogue(c, a, rq));
   const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
+  if (n > 1 && count > 0 && a.outMode == kOutSame && !a.residual && count * es <= c->layout.llSlotBytes / 2) {
+    TuneChoice pre = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, true, false);
+    if ((rq.algo >= 0 ? rq.algo : pre.algo) == FLAGCX_ALGO_LL) {
+      a.kind = kLlReduceScatter;
+      a.count = count;
+      a.inStride = count * es;
+      setIn(c, a, BufView(), rq.send);
+      setOut(c, a, BufView(), rq.recv);
+      setExtents(a, count * es * n, count * es);
+      note(c, flagcxCommOpReduceScatter, count * es * n, FLAGCX_ALGO_LL, 0);
+      return launchLl(c, a, count * es, stream);
+    }
+  }
   UserBuf uin;
   FCXCHECK(resolve(c, rq.send, count * es * n, 0, stream, &uin));
   const bool inVis = uin.visible();
@@ -520,6 +547,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   TuneChoice ch = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, inVis, nvlsOk);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PULL;
+  if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_PULL; // not eligible above
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpReduceScatter, count * es * n, algo, nCtas);
   if (algo == FLAGCX_ALGO_RING && n > 1 && a.outMode == kOutSame && !a.residual) {
@@ -529,6 +557,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
     const size_t slot = setRing(c, probe, es, 0);
     if (count <= slot) {
       a.count = count;
+      setExtents(a, count * es * n, count * oes);
       setRing(c, a, es, n - 1);
       setIn(c, a, BufView(), uin.local);
       setOut(c, a, BufView(), rq.recv);
@@ -540,6 +569,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
     a.kind = algo == FLAGCX_ALGO_NVLS ? kReduceScatterNvls : kReduceScatter;
     a.count = count;
     a.inStride = count * es;
+    setExtents(a, count * es * n, count * oes);
     applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
     return launch(c, algo == FLAGCX_ALGO_NVLS ? kFamNvls : kFamReduce, a, nCtas, stream);
@@ -578,6 +608,7 @@ flagcxResult_t reduceToRoot(flagcxComm *c, const DeviceCollRequest &rq, cudaStre
   note(c, flagcxCommOpReduce, count * es, FLAGCX_ALGO_PULL, nCtas);
   if (inVis) {
     a.count = count;
+    setExtents(a, count * es, count * oes);
     applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
     return launch(c, kFamReduce, a, nCtas, stream);
@@ -626,15 +657,18 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   const bool sendEverywhere = rq.op != flagcxCommOpBroadcast && rq.op != flagcxCommOpScatter;
   const bool recvEverywhere = rq.op != flagcxCommOpGather;
   const bool iAmRoot = me == rq.root;
-  if (rq.op == flagcxCommOpAllGather && n > 1 && blk > 0 && blk <= c->layout.llSlotBytes / 2) {
+  if ((rq.op == flagcxCommOpAllGather || rq.op == flagcxCommOpAlltoAll) && n > 1 && blk > 0 &&
+      blk <= c->layout.llSlotBytes / 2) {
     TuneChoice pre = c->tuner->choose(rq.op, recvBytes, n, true, false);
     if ((rq.algo >= 0 ? rq.algo : pre.algo) == FLAGCX_ALGO_LL) {
-      a.kind = kLlAllGather;
+      a.kind = rq.op == flagcxCommOpAllGather ? kLlAllGather : kLlAllToAll;
       a.count = blk;
+      a.inStride = blk;
       a.outStride = blk;
       setIn(c, a, BufView(), rq.send);
       setOut(c, a, BufView(), rq.recv);
       note(c, rq.op, recvBytes, FLAGCX_ALGO_LL, 0);
+      setExtents(a, sendBytes, recvBytes);
       return launchLl(c, a, blk, stream);
     }
   }
@@ -691,6 +725,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   }
   if (ringWanted && outVis) {
     a.kind = kAllGatherRing;
+    setExtents(a, sendBytes, recvBytes);
     a.count = blk;
     a.inStride = blk;
     a.outStride = blk;
@@ -702,6 +737,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   }
   if (algo == FLAGCX_ALGO_PUSH) {
     a.kind = pushKind;
+    setExtents(a, sendBytes, recvBytes);
     a.count = blk;
     a.inStride = blk;
     a.outStride = blk;
@@ -713,6 +749,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   }
   a.kind = pullKind;
   if (inVis) {
+    setExtents(a, sendBytes, recvBytes);
     a.count = blk;
     a.inStride = blk;
     a.outStride = blk;
@@ -773,6 +810,7 @@ flagcxResult_t allToAllv(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
     }
     applyIn(c, a, uin);
     setOut(c, a, BufView(), rq.recv);
+    setExtents(a, sendSpan, recvSpan);
     // Every rank must launch the same grid (CTA b meets CTA b of its peers), but the byte
     // counts differ from rank to rank: the count cannot follow the size here.
     TuneChoice ch;

@@ -15,9 +15,11 @@ struct flagcxMoe {
   int maxTokens, hidden, topk, nExperts, epr;
   size_t capacity;
   // symmetric
-  void *recv = nullptr, *expertOut = nullptr, *table = nullptr;
-  Window *wRecv = nullptr, *wOut = nullptr, *wTable = nullptr;
-  bool vmm[3] = {false, false, false};
+  void *recv = nullptr, *expertOut = nullptr, *table = nullptr, *dup = nullptr;
+  Window *wRecv = nullptr, *wOut = nullptr, *wTable = nullptr, *wDup = nullptr;
+  bool vmm[4] = {false, false, false, false};
+  int dupRecordsPerSender = 0;
+  size_t dupCountOff = 0; // byte offset of the count table inside `dup`
   // local
   int *pos = nullptr, *route = nullptr, *expertOffsets = nullptr;
   int lastTokens = 0;
@@ -61,7 +63,12 @@ void fillArgs(flagcxMoe *m, MoeArgs &a, int nTokens) {
     a.countsAll[p] = (int *)m->wTable->peer[p];
     a.recv[p] = (char *)m->wRecv->peer[p];
     a.expertOut[p] = (char *)m->wOut->peer[p];
+    a.dupList[p] = (int2 *)m->wDup->peer[p];
+    a.dupCount[p] = (int *)((char *)m->wDup->peer[p] + m->dupCountOff);
   }
+  a.dupRecordsPerSender = m->dupRecordsPerSender;
+  a.maxT = m->maxTokens;
+  a.dedup = readParam("MOE_DEDUP", 1) != 0 ? 1 : 0;
   a.pos = m->pos;
   a.route = m->route;
   a.expertOffsets = m->expertOffsets;
@@ -117,6 +124,13 @@ flagcxResult_t flagcxMoeCreate(flagcxComm_t comm, int maxTokens, int hidden, int
   if (r == flagcxSuccess) r = symAlloc(comm, rows, &m->expertOut, &m->wOut, &m->vmm[1]);
   if (r == flagcxSuccess)
     r = symAlloc(comm, alignUp(sizeof(int) * (size_t)comm->nranks * nExperts, 4096), &m->table, &m->wTable, &m->vmm[2]);
+  // duplicate records: per sender (maxTokens + one token per possible CTA) x (topk - 1),
+  // then the [sender][CTA] count table
+  m->dupRecordsPerSender = (maxTokens + FLAGCX_COLL_BARRIER_SLOTS) * std::max(1, topk - 1);
+  m->dupCountOff = alignUp((size_t)comm->nranks * m->dupRecordsPerSender * sizeof(int2), 4096);
+  if (r == flagcxSuccess)
+    r = symAlloc(comm, m->dupCountOff + alignUp(sizeof(int) * (size_t)comm->nranks * FLAGCX_COLL_BARRIER_SLOTS, 4096),
+                 &m->dup, &m->wDup, &m->vmm[3]);
   if (r != flagcxSuccess) { delete m; return r; }
   size_t items = (size_t)maxTokens * topk;
   FCX_CUDACHECK(cudaMalloc((void **)&m->pos, sizeof(int) * items));
@@ -136,6 +150,7 @@ flagcxResult_t flagcxMoeDestroy(flagcxMoe_t m) {
   symFree(c, m->recv, m->wRecv, m->vmm[0]);
   symFree(c, m->expertOut, m->wOut, m->vmm[1]);
   symFree(c, m->table, m->wTable, m->vmm[2]);
+  symFree(c, m->dup, m->wDup, m->vmm[3]);
   cudaFree(m->pos);
   cudaFree(m->route);
   cudaFree(m->expertOffsets);
@@ -160,9 +175,7 @@ flagcxResult_t flagcxMoeDispatch(flagcxMoe_t m, const void *x, const int *topkId
   fillArgs(m, a, nTokens);
   a.x = (const __nv_bfloat16 *)x;
   a.topkIdx = topkIdx;
-  int *myCounts = a.countsAll[c->rank] + (size_t)c->rank * m->nExperts;
-  cudaError_t e = launchMoeCount(s, topkIdx, myCounts, m->pos, nTokens * m->topk, m->nExperts, c->statusDev);
-  if (e != cudaSuccess) { FCX_WARN("moe count launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
+  cudaError_t e;
   m->lastTokens = nTokens;
   m->lastIdx = topkIdx;
   c->stats[flagcxCommOpAlltoAllv].calls++;

@@ -15,7 +15,7 @@
 //     is now mapped IN THE PEER'S address space;
 //   * the collective kernel of the owning rank then publishes "my input/output is at
 //     address X in your address space" to each peer before the kernel's first
-//     barrier (see exchangePointers in kernels/collectives.cu), so no rank ever needs
+//     barrier (publishPointers / learnPointers in kernels/coll_common.cuh), so no rank ever needs
 //     to know on the host where a peer's buffer lives.
 //
 // Because the peers' main threads take no part, ranks need not meet a new allocation

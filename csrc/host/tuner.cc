@@ -69,6 +69,7 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       break;
     }
     case flagcxCommOpReduceScatter:
+      if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
       ch.algo = nvlsOk && nranks > 2 && bytes >= (1u << 20) ? FLAGCX_ALGO_NVLS : FLAGCX_ALGO_PULL;
       work = bytes / std::max(1, nranks);
       break;
@@ -76,8 +77,11 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
       ch.algo = FLAGCX_ALGO_PUSH;
       break;
-    case flagcxCommOpBroadcast:
     case flagcxCommOpAlltoAll:
+      if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
+      ch.algo = FLAGCX_ALGO_PUSH;
+      break;
+    case flagcxCommOpBroadcast:
       ch.algo = FLAGCX_ALGO_PUSH; // the launcher falls back to pull when the output is not registered
       break;
     default:
@@ -123,7 +127,7 @@ std::string Tuner::toJson() const {
     firstEntry = false;
     o << "    {\"op\": " << op << ", \"bucket\": " << rest / 2 << ", \"registered\": " << rest % 2
       << ", \"algo\": " << kv.second.algo << ", \"nctas\": " << kv.second.nCtas << ", \"usec\": " << kv.second.usec
-      << "}";
+      << ", \"best_usec\": " << kv.second.bestUsec << "}";
   }
   o << "\n  ]\n}\n";
   return o.str();
@@ -149,6 +153,7 @@ flagcxResult_t Tuner::fromJson(const std::string &text) {
     ch.algo = (int)field("algo", -1);
     ch.nCtas = (int)field("nctas", 0);
     ch.usec = (float)field("usec", 0);
+    ch.bestUsec = (float)field("best_usec", 0);
     if (op < 0 || op >= flagcxNumCommOps || bucket < 0 || bucket > 62 || ch.algo < 0 || ch.algo >= FLAGCX_ALGO_COUNT ||
         ch.nCtas < 1 || ch.nCtas > FLAGCX_COLL_BARRIER_SLOTS)
       return flagcxInvalidArgument;
@@ -222,7 +227,9 @@ std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, boo
       out.push_back({a, ctas});
     }
   // the barrier-free path picks its own CTA count
-  if (n > 1 && ((op == flagcxCommOpAllReduce && bytes <= llCap) || (op == flagcxCommOpAllGather && bytes / n <= llCap)))
+  if (n > 1 && ((op == flagcxCommOpAllReduce && bytes <= llCap) ||
+                ((op == flagcxCommOpAllGather || op == flagcxCommOpReduceScatter || op == flagcxCommOpAlltoAll) &&
+                 bytes / n <= llCap)))
     out.push_back({FLAGCX_ALGO_LL, 1});
   return out;
 }
@@ -303,6 +310,7 @@ flagcxResult_t Tuner::tune(flagcxComm *c, flagcxCommOp_t op, flagcxDataType_t dt
       TuneChoice ch;
       if (baseUs > 0 && bestUs >= 0.95f * baseUs) { ch = base; ch.usec = baseUs; } // hysteresis
       else { ch.algo = best.algo; ch.nCtas = best.nCtas; ch.usec = bestUs; }
+      ch.bestUsec = bestUs;
       table[keyOf(op, bucketOf(bytes), registered != 0)] = ch;
       if (c->rank == 0)
         FCX_INFO(SUB_TUNING, "%s %zu B %s: algo %d ctas %d %.1f us (heuristic %.1f us)", commOpName(op), bytes,

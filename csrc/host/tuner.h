@@ -22,7 +22,9 @@ namespace fcx {
 struct TuneChoice {
   int algo = FLAGCX_ALGO_AUTO;
   int nCtas = 0;
-  float usec = 0.f; // measured time of the winner (0: heuristic)
+  float usec = 0.f;     // measured time of this choice (0: heuristic, never measured)
+  float bestUsec = 0.f; // fastest candidate measured for the bucket (the choice may be the
+                        // heuristic's when that is within 5 % of it)
 };
 
 struct Tuner {

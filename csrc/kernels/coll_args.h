@@ -34,6 +34,8 @@ enum CollKind : int {
   kAllReduceTwoShotCast, // reduce own slice into local 16-bit scratch, then pull all slices and widen to fp32
   kLlAllReduce,          // small messages: data+flag stores into per-sender slots, no barrier
   kLlAllGather,
+  kLlReduceScatter,      // block p of the input goes to rank p, which reduces what it receives
+  kLlAllToAll,           // block p of the input goes to rank p's output block `rank`
   kAllGatherRing,        // n-1 steps: forward the block received in the previous step to the next rank
   kReduceScatterRing,    // n-1 steps: add the own block to the partial sum received and pass it on
   kAllReduceRing,        // ring reduce-scatter into the output, then ring all-gather of it
@@ -99,6 +101,10 @@ struct CollArgs {
   uint32_t llPad;
   uint32_t xchg;       // XchgBits
   uint32_t xchgParity; // alternates between consecutive exchanging launches of a communicator
+  // Bytes every rank's input / output region spans from in[p] / out[p] (0: not known).
+  // Only the bounds-checking build (FLAGCX_BOUNDS_CHECK) reads them: before its main
+  // phase a kernel verifies that everything it is about to touch lies inside.
+  size_t inBytes, outBytes;
   size_t count;        // elements: total (allreduce, reduce, broadcast) or per rank-block
   // Rank-blocks inside the in/out buffers start at multiples of these byte strides
   // (reduce-scatter, gather, scatter, allgather, alltoall).

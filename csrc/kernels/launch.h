@@ -22,8 +22,6 @@ struct LaunchCtx {
 };
 
 struct MoeArgs;
-cudaError_t launchMoeCount(cudaStream_t s, const int *topkIdx, int *counts, int *pos, int items, int nExperts,
-                           flagcxDevStatus *status);
 cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a);
 cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a);
 

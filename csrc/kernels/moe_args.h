@@ -21,6 +21,15 @@ struct MoeArgs {
   char *recv[FLAGCX_MAX_RANKS];      // recv[p]: rank p's receive buffer [capacity, H] bf16
   char *expertOut[FLAGCX_MAX_RANKS]; // expertOut[p]: rank p's expert outputs, same row order
   int *expertOffsets;      // local [EPR + 1]: row range of each local expert
+  // A token that goes to several experts of one rank crosses NVLink once: the first copy
+  // lands in its final row, and a (source row, destination row) record asks the receiver
+  // to make the other copies locally.  dupList[p] / dupCount[p]: rank p's record area
+  // [sender][CTA][dupCapPerCta] and count table [sender][CTA], as mapped here.
+  int2 *dupList[FLAGCX_MAX_RANKS];
+  int *dupCount[FLAGCX_MAX_RANKS];
+  int dupRecordsPerSender; // records reserved per sender in a rank's area
+  int maxT;                // largest token count any rank may pass (fixes the per-CTA share of that area)
+  int dedup;               // 0: every (token, expert) pair crosses NVLink on its own
   int T, H, K, E, EPR;
   size_t capacity;         // rows in recv / expertOut
 };

@@ -280,6 +280,22 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint4 *stg = s.epi[warp - 2];
     int acc = 0;
     uint32_t accPhase = 0;
+    // reduce-scatter: a tile sent to a peer is counted in on that peer one tile later, when
+    // its TMA stores have long completed, so the epilogue never sits out an NVLink round trip
+    int pendOwner = -1, pendRb = 0;
+    // Every epilogue warp counts its own quarter of the tile in (the owner waits for four
+    // arrivals per tile): no barrier between the warps, so a warp that gives up after a
+    // timed-out wait can never leave the others stuck.
+    auto countInPending = [&](bool fourNewerGroups) {
+      if (pendOwner < 0) return;
+      if (lane == 0) {
+        if (fourNewerGroups) bulkWaitDone<BN / kEpiCols>(); else bulkWaitDone<0>();
+        fenceProxyAsync();
+        fcxdev::fenceSys();
+        fcxdev::redAddReleaseSys(a.rowFlags[pendOwner] + kFlagStride * pendRb, 1ull);
+      }
+      pendOwner = -1;
+    };
     for (int tile = unit; tile < nTiles; tile += units) {
       int tm, tn;
       tileCoords(a, rank, tile, tilesN, TM, &tm, &tn);
@@ -310,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             if (lane == 0)
               ok = waitFlagGe(c, a.rowFlags[rank] + kFlagStride * (rowLocal / BM),
-                              a.epoch * (unsigned long long)((n - 1) * tilesN), abortFlag, 0xffffffffu);
+                              a.epoch * (unsigned long long)((n - 1) * tilesN * 4), abortFlag, 0xffffffffu);
             if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
             others = a.partial[rank] + rowLocal * a.N + (size_t)tn * BN;
           }
@@ -398,17 +414,60 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (PAIR && !leader) mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
         else mbarArrive(&s.tmemEmpty[acc]);
       }
-      if (a.mode == kGemmReduceScatter && owner != rank) {
-        // count the tile in on its owner once all four epilogue warps' stores are complete
-        if (lane == 0) { bulkWaitDone<0>(); fenceProxyAsync(); }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          fcxdev::fenceSys();
-          const int rbLocal = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
-          fcxdev::redAddReleaseSys(a.rowFlags[owner] + kFlagStride * rbLocal, 1ull);
+      if (a.mode == kGemmReduceScatter) {
+        // the previous remote tile: this tile put four newer store groups behind it, or none
+        countInPending(tmaOut);
+        if (owner != rank) {
+          pendOwner = owner;
+          pendRb = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
         }
       }
       if (++acc == 2) { acc = 0; accPhase ^= 1; }
+    }
+    countInPending(false);
+  } else if (warp >= 6 && a.mode == kAllGatherGemm && n > 1 && a.pushThreads) {
+    // ---- pusher, thread flavour: warps 6 and 7 of EVERY CTA copy this CTA's share of each
+    // 128-row chunk of my shard to all peers with plain 16-byte loads and posted stores
+    // (eight loads in flight per thread), chunk 0 first, and count the chunk in on every
+    // peer once: one fence and one atomic per peer, chunk and CTA. ----
+    const int pt = threadIdx.x - 192; // 0..63
+    const int chunks = a.rowsPerRank / BM;
+    const size_t chunkVecs = (size_t)BM * a.K * 2 / 16;
+    const size_t shardVec0 = (size_t)rank * a.rowsPerRank * a.K * 2 / 16;
+    const size_t per = (chunkVecs + G - 1) / G;
+    const size_t vb = (size_t)blockIdx.x * per < chunkVecs ? (size_t)blockIdx.x * per : chunkVecs;
+    const size_t ve = vb + per < chunkVecs ? vb + per : chunkVecs;
+    const uint4 *src = (const uint4 *)a.gathered[rank] + shardVec0;
+    // (no wait in here and none on the abort flag: both warps run the same number of rounds)
+    for (int ch = 0; ch < chunks; ++ch) {
+      const size_t c0 = (size_t)ch * chunkVecs;
+      size_t i = vb + pt;
+      for (; i + 7 * 64 < ve; i += 8 * 64) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = src[c0 + i + u * 64];
+        for (int k = 1; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          uint4 *dst = (uint4 *)a.gathered[p] + shardVec0 + c0;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) st16(dst + i + u * 64, v[u]);
+        }
+      }
+      for (; i < ve; i += 64) {
+        const uint4 v = src[c0 + i];
+        for (int k = 1; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          st16((uint4 *)a.gathered[p] + shardVec0 + c0 + i, v);
+        }
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory"); // both pusher warps have issued their stores
+      if (pt == 0) {
+        fcxdev::fenceSys();
+        for (int k = 1; k < n; ++k) {
+          int p = rank + k; if (p >= n) p -= n;
+          redAddRelaxedSys(a.chunkFlags[p] + kFlagStride * ((size_t)rank * chunks + ch), 1ull);
+        }
+      }
     }
   } else if (warp == 6 && a.mode == kAllGatherGemm && n > 1) {
     // ---- pusher: one thread drives the copy engine.  My shard goes out in 4 KiB

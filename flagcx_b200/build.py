@@ -35,8 +35,21 @@ def build_devtest(verbose: bool = False) -> str:
     return lib
 
 
+def build_bounds(jobs: int | None = None, verbose: bool = False) -> str:
+    """The kernels once more with -DFLAGCX_BOUNDS_CHECK (csrc/build/bounds/libflagcx.so): every
+    kernel verifies the extent of its accesses first; tests/test_gpu_bounds_build.py runs
+    the emulated-world suite against it."""
+    jobs = jobs or os.cpu_count() or 4
+    res = subprocess.run(["make", "-C", os.path.join(ROOT, "csrc"), f"-j{jobs}", "bounds"], capture_output=not verbose, text=True)
+    if res.returncode != 0:
+        sys.stderr.write((res.stdout or "") + (res.stderr or ""))
+        raise RuntimeError("building the bounds-checking libflagcx.so failed")
+    return os.path.join(ROOT, "csrc", "build", "bounds", "libflagcx.so")
+
+
 def build(verbose: bool = False) -> None:
     build_core(verbose=verbose)
+    build_bounds(verbose=verbose)
     build_devtest(verbose=verbose)
     try:
         from flagcx_b200.torch_backend import build as tb

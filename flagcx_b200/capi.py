@@ -16,7 +16,8 @@ from typing import Optional, Sequence
 import numpy as np
 
 _LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
-LIB_PATH = os.path.join(_LIB_DIR, "libflagcx.so")
+# FLAGCX_LIBRARY selects another build of the library (sanitizer or bounds-checking builds)
+LIB_PATH = os.environ.get("FLAGCX_LIBRARY") or os.path.join(_LIB_DIR, "libflagcx.so")
 
 # ---- enums (flagcx.h) --------------------------------------------------------
 flagcxSuccess = 0

@@ -31,32 +31,31 @@ class PipelineStage:
         self.dtype, self.device = dtype, torch.device(device)
 
     # -- transfers ------------------------------------------------------------------
-    def _sync(self):
-        if self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()
+    def _stream(self):
+        """CUDA stages queue their transfers on torch's current stream: the order with the
+        stage's compute is the stream's, and the host never waits."""
+        return torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
 
     def _send(self, t: torch.Tensor, peer: int):
         t = t.contiguous()
-        self.comm.send(t, t.numel(), _DT[t.dtype], peer)
-        self._sync()
+        self.comm.send(t, t.numel(), _DT[t.dtype], peer, stream=self._stream())
 
     def _recv(self, shape, peer: int) -> torch.Tensor:
         t = torch.empty(shape, dtype=self.dtype, device=self.device)
-        self.comm.recv(t, t.numel(), _DT[t.dtype], peer)
-        self._sync()
+        self.comm.recv(t, t.numel(), _DT[t.dtype], peer, stream=self._stream())
         return t
 
     def _exchange(self, send: torch.Tensor | None, send_peer: int, recv_shape, recv_peer: int):
         """A send and a receive that may cross: issued as one group so neither blocks the other."""
         out = torch.empty(recv_shape, dtype=self.dtype, device=self.device) if recv_shape is not None else None
+        st = self._stream()
         self.comm.group_start()
         if send is not None:
             send = send.contiguous()
-            self.comm.send(send, send.numel(), _DT[send.dtype], send_peer)
+            self.comm.send(send, send.numel(), _DT[send.dtype], send_peer, stream=st)
         if out is not None:
-            self.comm.recv(out, out.numel(), _DT[out.dtype], recv_peer)
+            self.comm.recv(out, out.numel(), _DT[out.dtype], recv_peer, stream=st)
         self.comm.group_end()
-        self._sync()
         return out
 
     # -- schedule -------------------------------------------------------------------

@@ -22,7 +22,7 @@ from flagcx_b200.utils.dist import init_world
 
 OPS = {"allreduce": capi.OP_ALLREDUCE, "allgather": capi.OP_ALLGATHER, "reducescatter": capi.OP_REDUCESCATTER,
        "alltoall": capi.OP_ALLTOALL}
-ALGO_NAMES = ["oneshot", "twoshot", "nvls_oneshot", "nvls_twoshot", "push", "pull", "nvls"]
+ALGO_NAMES = ["oneshot", "twoshot", "nvls_oneshot", "nvls_twoshot", "push", "pull", "nvls", "ll", "ring"]
 
 
 def parse_size(s: str) -> int:
@@ -62,6 +62,14 @@ def main() -> int:
             mark = "" if tuple(new) == tuple(old) else "   *"
             print(f"{name:>13} {size:>11}  {ALGO_NAMES[old[0]]}/{old[1]} -> {ALGO_NAMES[new[0]]}/{new[1]}{mark}")
         print(f"wrote {args.out}")
+        # every stored choice against the fastest candidate measured for its bucket
+        import json
+        worst = 1.0
+        for e in json.load(open(args.out))["entries"]:
+            if e.get("best_usec", 0) > 0 and e.get("usec", 0) > 0:
+                worst = max(worst, e["usec"] / e["best_usec"])
+        print(f"slowest stored choice relative to the best candidate measured for its size: {worst:.3f}x "
+              f"({'within' if worst <= 1.0 / 0.95 + 1e-6 else 'NOT within'} the 5 % hysteresis)")
     w.comm.barrier()
     w.comm.destroy()
     return 0

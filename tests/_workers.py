@@ -763,18 +763,25 @@ def _pp_stage_module(stage, width):
     return torch.nn.Sequential(lin, torch.nn.Tanh())
 
 
-def pp_1f1b(rank, n, uid, n_micro, width):
-    """1F1B over n stages on CPU tensors against the same model run in one process."""
+def pp_1f1b(rank, n, uid, n_micro, width, use_cuda=False):
+    """1F1B over n stages (CPU tensors, or one GPU per stage) against the same model run
+    in one process."""
     import torch
     from flagcx_b200.parallel.pp import PipelineStage
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
     batch = 4
     g = torch.Generator().manual_seed(7)
     xs = [torch.randn(batch, width, generator=g) for _ in range(n_micro)]
     ts = [torch.randn(batch, width, generator=g) for _ in range(n_micro)]
-    stage = PipelineStage(comm, _pp_stage_module(rank, width), None if rank == 0 else (batch, width), (batch, width))
+    stage = PipelineStage(comm, _pp_stage_module(rank, width).to(dev), None if rank == 0 else (batch, width),
+                          (batch, width), device=dev)
     loss = stage.run_1f1b(xs if rank == 0 else None, n_micro,
-                          (lambda y, i: ((y - ts[i]) ** 2).mean() / n_micro) if rank == n - 1 else None)
+                          (lambda y, i: ((y - ts[i].to(dev)) ** 2).mean() / n_micro) if rank == n - 1 else None)
+    if use_cuda:
+        torch.cuda.synchronize()
     # reference: the whole model here
     full = [_pp_stage_module(s, width) for s in range(n)]
     ref_loss = 0.0
@@ -786,8 +793,8 @@ def pp_1f1b(rank, n, uid, n_micro, width):
         l.backward()
         ref_loss += float(l)
     mine, ref = stage.module[0], full[rank][0]
-    out = {"grad_w": float((mine.weight.grad - ref.weight.grad).abs().max()),
-           "grad_b": float((mine.bias.grad - ref.bias.grad).abs().max())}
+    out = {"grad_w": float((mine.weight.grad.cpu() - ref.weight.grad).abs().max()),
+           "grad_b": float((mine.bias.grad.cpu() - ref.bias.grad).abs().max())}
     if rank == n - 1:
         out["loss"] = abs(loss - ref_loss)
     comm.barrier()
@@ -866,13 +873,17 @@ def gpu_buffers_over_sockets(rank, n, uid):
 # ---------------------------------------------------------------------------
 # sequence / context parallelism
 # ---------------------------------------------------------------------------
-def sp_ulysses_and_ring(rank, n, uid, S, H, D):
-    """Ulysses re-sharding and ring attention on CPU tensors against full attention."""
+def sp_ulysses_and_ring(rank, n, uid, S, H, D, use_cuda=False):
+    """Ulysses re-sharding and ring attention (CPU tensors, or one GPU per rank) against
+    full attention."""
     import torch
     from flagcx_b200.parallel.sp import Ulysses, ring_attention
+    if use_cuda:
+        torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
     g = torch.Generator().manual_seed(11)
-    q, k, v = (torch.randn(S, H, D, generator=g) for _ in range(3))
+    q, k, v = (torch.randn(S, H, D, generator=g).to(dev) for _ in range(3))
     s = S // n
     mine = slice(rank * s, (rank + 1) * s)
     out = {}
@@ -885,7 +896,7 @@ def sp_ulysses_and_ring(rank, n, uid, S, H, D):
     def full_attention(causal):
         sc = torch.einsum("shd,thd->hst", q, k) / D ** 0.5
         if causal:
-            sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), -float("inf"))
+            sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=dev).tril(), -float("inf"))
         return torch.einsum("hst,thd->shd", sc.softmax(-1), v)
 
     for causal in (False, True):

@@ -253,6 +253,29 @@ def test_ring_algorithms(n, exchange):
             del os.environ["FLAGCX_EMU_EXCHANGE"]
 
 
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_small_reduce_scatter_and_alltoall_without_barrier(n):
+    comms = world(n)
+    for dt in (capi.FLOAT, capi.BFLOAT16):
+        for count in (1, 3, 257, 1024):
+            xs = make_inputs(n, count * n, dt)
+            ref = reference(xs, capi.SUM)
+            rs = [torch.zeros(count, dtype=TORCH_DT[dt], device="cuda") for _ in range(n)]
+            aa = [torch.zeros(count * n, dtype=TORCH_DT[dt], device="cuda") for _ in range(n)]
+            for _ in range(2):  # both slot parities
+                for r in range(n):
+                    comms[r].reduce_scatter_fused(xs[r], rs[r], count, dt, capi.SUM, algo=capi.ALGO_LL)
+                for r in range(n):
+                    comms[r].all_to_all(xs[r], aa[r], count, dt)  # small blocks: the heuristic's own choice
+            torch.cuda.synchronize()
+            assert_no_device_error(comms)
+            assert comms[0].stats(capi.OP_REDUCESCATTER).lastAlgo == capi.ALGO_LL
+            assert comms[0].stats(capi.OP_ALLTOALL).lastAlgo == capi.ALGO_LL
+            for r in range(n):
+                check_close(rs[r], ref[r * count:(r + 1) * count], dt, n, f"LL reduce-scatter count {count} rank {r}")
+                assert torch.equal(aa[r], torch.cat([xs[p][r * count:(r + 1) * count] for p in range(n)])), "LL alltoall"
+
+
 def test_small_allgather_without_barrier():
     n = 4
     comms = world(n)

@@ -73,6 +73,26 @@ def test_two_level_route_when_one_machine_poses_as_several_nodes():
 
 
 @needs2
+def test_pipeline_1f1b_with_one_gpu_per_stage():
+    n = 4 if ngpus() >= 4 else 2
+    res = run_ranks(n, "pp_1f1b", 6, 64, True, timeout=300)
+    for rank, out in res.items():
+        assert all(v < 1e-4 for v in out.values()), (rank, out)
+
+
+@needs2
+def test_ulysses_and_ring_attention_on_gpus():
+    """Sequence parallelism over NVLink: the all-to-all re-sharding is exact, ring attention
+    (next block in flight on a side stream during the block's attention) matches full
+    attention computed on one GPU."""
+    n = 4 if ngpus() >= 4 else 2
+    res = run_ranks(n, "sp_ulysses_and_ring", 64 * n, 8, 32, True, timeout=300)
+    for rank, out in res.items():
+        assert out["seq_to_heads"] == 0.0 and out["roundtrip"] == 0.0, (rank, out)
+        assert out["ring_causal0"] < 1e-4 and out["ring_causal1"] < 1e-4, (rank, out)
+
+
+@needs2
 def test_missing_peer_becomes_an_error_code():
     n = 2
     env = {"NCCL_NVLS_ENABLE": "0", "FLAGCX_NVLS_ENABLE": "0"}
