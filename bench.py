@@ -17,6 +17,7 @@ torch FSDP on the same model shape (see baseline/reference_arm.py).
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import subprocess
@@ -102,6 +103,8 @@ def run_ours(args) -> dict:
         assert comm.device_path, "expected the NVLink device path"
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny()
+    if args.layers:
+        cfg = dataclasses.replace(cfg, n_layers=args.layers)
     seq = args.seq_len
     ops.assume_unit_loss_grad = True
     model = ShardedModel(build_units(cfg), comm, rank, world, dev)
@@ -180,7 +183,8 @@ def run_ours(args) -> dict:
         "dtype": "bf16",
         "data": "synthetic uniform-random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
-        "config": {"model": args.model, "global_batch": world, "seq_len": seq, "parallelism": f"fsdp{world}",
+        "config": {"model": args.model + (f"[layers={args.layers}: a cut-down profiling run, not the headline]" if args.layers else ""),
+                   "global_batch": world, "seq_len": seq, "parallelism": f"fsdp{world}",
                    "optimizer": "AdamW, fused kernel, bf16 states",
                    "l2": "no flush needed: each step streams 16 GB of parameters plus activations, far above the 126 MB L2"},
         "backend": "flagcx (NVLink kernels of this repository)" if world > 1 else "single GPU, no collectives",
@@ -209,6 +213,9 @@ def main():
                          "ProcessGroup / over NCCL")
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling only (--impl ours): keep this many decoder layers so that a launch list stays short; "
+                         "the result names the cut in config.model and is not the headline number")
     ap.add_argument("--trace-comm", default="", help="write rank 0's per-collective trace of the timed steps (JSON) here; "
                                                      "summarise it with bench/trace_summary.py")
     args = ap.parse_args()

@@ -3,7 +3,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29502 bench/cta_sweep.py --bytes 436M --out sweep.jsonl
 
-Times all-gather (push) and reduce-scatter (pull) of one total message size on
+Times all-gather (push) and reduce-scatter (pull), and with --ops allreduce the two-shot
+all-reduce over peer loads and over the switch (multimem), of one total message size on
 registered windows for a list of CTA counts, each both on the per-thread load/store
 path and on the bulk-copy-engine path (FLAGCX_BULK_COPY / FLAGCX_BULK_REDUCE switched per
 row).  Collectives that run beside GEMMs (sharded training) should take the smallest
@@ -53,6 +54,9 @@ def main():
     ap.add_argument("--bytes", default="436M", help="total message (all ranks' blocks together)")
     ap.add_argument("--ctas", default="2,4,8,12,16,24,32,48,96")
     ap.add_argument("--iters", type=int, default=7)
+    ap.add_argument("--ops", default="allgather,reducescatter",
+                    help="also: allreduce (two-shot over peer loads, and the switch-reduced two-shot when the "
+                         "communicator has a multicast binding, i.e. under FLAGCX_NVLS_ENABLE=1)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     w = init_world()
@@ -68,7 +72,19 @@ def main():
     if rank == 0:
         print(f"# world {n}  total {total * 2} bytes  per-rank block {per * 2} bytes", flush=True)
         print(f"{'op':>14} {'path':>7} {'ctas':>5} {'us':>9} {'busGB/s':>9}", flush=True)
-    for op in ("allgather", "reducescatter"):
+    ops = args.ops.split(",")
+    if "allreduce" in ops:
+        algos = [("twoshot", capi.ALGO_TWOSHOT)] + ([("nvls", capi.ALGO_NVLS_TWOSHOT)] if w.comm.has_multicast() else [])
+        for path, algo in algos:
+            for ctas in [int(x) for x in args.ctas.split(",")]:
+                fn = lambda: w.comm.all_reduce_fused(src, dst, total, capi.BFLOAT16, capi.SUM, algo=algo, nctas=ctas)
+                us = timed(fn, args.iters)
+                assert w.comm.async_error() == 0, w.comm.last_error()
+                bw = total * 2 / us / 1e3 * 2 * (n - 1) / n
+                rows.append({"op": "allreduce", "path": path, "ctas": ctas, "us": us, "busbw": bw, "n_gpus": n, "bytes": total * 2})
+                if rank == 0:
+                    print(f"{'allreduce':>14} {path:>7} {ctas:>5} {us:>9.1f} {bw:>9.1f}", flush=True)
+    for op in [o for o in ops if o in ("allgather", "reducescatter")]:
         for path in ("threads", "engine"):
             os.environ["FLAGCX_BULK_COPY"] = os.environ["FLAGCX_BULK_REDUCE"] = "1" if path == "engine" else "0"
             os.environ["FLAGCX_BULK_COPY_MIN_BYTES"] = "1"

@@ -12,7 +12,7 @@ import argparse
 import json
 from collections import defaultdict
 
-ALGO = {-1: "-", 0: "oneshot", 1: "twoshot", 2: "nvls1", 3: "nvls2", 4: "push", 5: "pull", 6: "nvls", 7: "ll", 8: "ring"}
+ALGO = {-1: "-", 0: "oneshot", 1: "twoshot", 2: "nvls1", 3: "nvls2", 4: "push", 5: "pull", 6: "nvls", 7: "ll", 8: "ring", 9: "ce"}
 
 
 def main():

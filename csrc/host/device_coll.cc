@@ -705,6 +705,11 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PUSH;
   if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_PUSH; // not eligible above
+  // Copy-engine all-gather: needs every rank's output inside a window (the host must know
+  // the peers' addresses) and real peers.
+  const bool ceWanted = algo == FLAGCX_ALGO_COPY_ENGINE && rq.op == flagcxCommOpAllGather && n > 1 && !c->emu &&
+                        uout.reach == kReachWindow && blk > 0;
+  if (algo == FLAGCX_ALGO_COPY_ENGINE && !ceWanted) algo = FLAGCX_ALGO_PUSH;
   const bool ringWanted = algo == FLAGCX_ALGO_RING && rq.op == flagcxCommOpAllGather && n > 1;
   if (algo == FLAGCX_ALGO_RING) algo = FLAGCX_ALGO_PUSH;
   if (algo == FLAGCX_ALGO_PUSH && !(outVis && pushKind >= 0)) algo = FLAGCX_ALGO_PULL;
@@ -713,6 +718,23 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   const int nCtas = pickCtas(c, rq, ch);
   note(c, rq.op, std::max(sendBytes, recvBytes), algo, nCtas);
 
+  if (ceWanted) {
+    // 1. a one-CTA barrier kernel: every rank has reached this call in its stream, so
+    //    nobody still reads the previous contents of its output;
+    // 2. n-1 peer copies and the local one, on the copy engines, nearest neighbour first
+    //    so that no rank is the target of all the others at once;
+    // 3. the barrier again: it starts after this rank's copies have completed (stream
+    //    order) and ends when every rank's have.
+    FCXCHECK(deviceBarrier(c, stream));
+    Window *w = uout.view.win;
+    for (int i = 0; i < n; ++i) {
+      const int p = (me + i) % n;
+      char *dst = (char *)w->peer[p] + uout.view.off + (size_t)me * blk;
+      if (p == me && dst == (const char *)rq.send) continue; // in place
+      FCX_CUDACHECK(cudaMemcpyAsync(dst, rq.send, blk, cudaMemcpyDeviceToDevice, stream));
+    }
+    return deviceBarrier(c, stream);
+  }
   if (algo == FLAGCX_ALGO_NVLS) {
     a.kind = kAllGatherNvls;
     a.dtype = flagcxFloat32; // multimem.st moves raw 16-byte packs

@@ -1,6 +1,6 @@
 // moe.cc -- host side of the expert-parallel dispatch/combine kernels: owns the
-// peer-mapped receive and expert-output buffers and the count tables, and launches
-// count -> dispatch, and combine.
+// peer-mapped receive, expert-output and partial-sum buffers, the count tables and the
+// group records, and launches dispatch and combine.
 #include <algorithm>
 
 #include "../kernels/launch.h"
@@ -15,13 +15,13 @@ struct flagcxMoe {
   int maxTokens, hidden, topk, nExperts, epr;
   size_t capacity;
   // symmetric
-  void *recv = nullptr, *expertOut = nullptr, *table = nullptr, *dup = nullptr;
-  Window *wRecv = nullptr, *wOut = nullptr, *wTable = nullptr, *wDup = nullptr;
-  bool vmm[4] = {false, false, false, false};
-  int dupRecordsPerSender = 0;
-  size_t dupCountOff = 0; // byte offset of the count table inside `dup`
+  void *recv = nullptr, *expertOut = nullptr, *table = nullptr, *grp = nullptr, *partial = nullptr;
+  Window *wRecv = nullptr, *wOut = nullptr, *wTable = nullptr, *wGrp = nullptr, *wPartial = nullptr;
+  bool vmm[5] = {false, false, false, false, false};
+  int grpRecordsPerSender = 0;
+  size_t grpCountOff = 0, wRowOff = 0; // byte offsets of the count table and the per-row weights inside `grp`
   // local
-  int *pos = nullptr, *route = nullptr, *expertOffsets = nullptr;
+  int *pos = nullptr, *route = nullptr, *expertOffsets = nullptr, *lead = nullptr;
   int lastTokens = 0;
   const int *lastIdx = nullptr;
 };
@@ -63,12 +63,16 @@ void fillArgs(flagcxMoe *m, MoeArgs &a, int nTokens) {
     a.countsAll[p] = (int *)m->wTable->peer[p];
     a.recv[p] = (char *)m->wRecv->peer[p];
     a.expertOut[p] = (char *)m->wOut->peer[p];
-    a.dupList[p] = (int2 *)m->wDup->peer[p];
-    a.dupCount[p] = (int *)((char *)m->wDup->peer[p] + m->dupCountOff);
+    a.grpList[p] = (int *)m->wGrp->peer[p];
+    a.grpCount[p] = (int *)((char *)m->wGrp->peer[p] + m->grpCountOff);
+    a.wRow[p] = (float *)((char *)m->wGrp->peer[p] + m->wRowOff);
+    a.partial[p] = (char *)m->wPartial->peer[p];
   }
-  a.dupRecordsPerSender = m->dupRecordsPerSender;
+  a.grpRecordsPerSender = m->grpRecordsPerSender;
   a.maxT = m->maxTokens;
   a.dedup = readParam("MOE_DEDUP", 1) != 0 ? 1 : 0;
+  a.preReduce = readParam("MOE_COMBINE_REDUCE", 1) != 0 ? 1 : 0;
+  a.lead = m->lead;
   a.pos = m->pos;
   a.route = m->route;
   a.expertOffsets = m->expertOffsets;
@@ -124,18 +128,21 @@ flagcxResult_t flagcxMoeCreate(flagcxComm_t comm, int maxTokens, int hidden, int
   if (r == flagcxSuccess) r = symAlloc(comm, rows, &m->expertOut, &m->wOut, &m->vmm[1]);
   if (r == flagcxSuccess)
     r = symAlloc(comm, alignUp(sizeof(int) * (size_t)comm->nranks * nExperts, 4096), &m->table, &m->wTable, &m->vmm[2]);
-  // duplicate records: per sender (maxTokens + one token per possible CTA) x (topk - 1),
-  // then the [sender][CTA] count table
-  m->dupRecordsPerSender = (maxTokens + FLAGCX_COLL_BARRIER_SLOTS) * std::max(1, topk - 1);
-  m->dupCountOff = alignUp((size_t)comm->nranks * m->dupRecordsPerSender * sizeof(int2), 4096);
+  // group records: per sender (maxTokens + one token per possible CTA) x topk records of
+  // FLAGCX_MOE_MAX_TOPK ints, then the [sender][CTA] count table, then one gate weight per
+  // received row
+  m->grpRecordsPerSender = (maxTokens + FLAGCX_COLL_BARRIER_SLOTS) * topk;
+  m->grpCountOff = alignUp((size_t)comm->nranks * m->grpRecordsPerSender * FLAGCX_MOE_MAX_TOPK * sizeof(int), 4096);
+  m->wRowOff = m->grpCountOff + alignUp(sizeof(int) * (size_t)comm->nranks * FLAGCX_COLL_BARRIER_SLOTS, 4096);
   if (r == flagcxSuccess)
-    r = symAlloc(comm, m->dupCountOff + alignUp(sizeof(int) * (size_t)comm->nranks * FLAGCX_COLL_BARRIER_SLOTS, 4096),
-                 &m->dup, &m->wDup, &m->vmm[3]);
+    r = symAlloc(comm, m->wRowOff + alignUp(sizeof(float) * capacityRows, 4096), &m->grp, &m->wGrp, &m->vmm[3]);
+  if (r == flagcxSuccess) r = symAlloc(comm, rows, &m->partial, &m->wPartial, &m->vmm[4]);
   if (r != flagcxSuccess) { delete m; return r; }
   size_t items = (size_t)maxTokens * topk;
   FCX_CUDACHECK(cudaMalloc((void **)&m->pos, sizeof(int) * items));
   FCX_CUDACHECK(cudaMalloc((void **)&m->route, sizeof(int) * items * 2));
   FCX_CUDACHECK(cudaMalloc((void **)&m->expertOffsets, sizeof(int) * (m->epr + 1)));
+  FCX_CUDACHECK(cudaMalloc((void **)&m->lead, sizeof(int) * items));
   FCX_CUDACHECK(cudaMemset(m->table, 0, sizeof(int) * (size_t)comm->nranks * nExperts));
   FCX_CUDACHECK(cudaDeviceSynchronize());
   *out = m;
@@ -150,10 +157,12 @@ flagcxResult_t flagcxMoeDestroy(flagcxMoe_t m) {
   symFree(c, m->recv, m->wRecv, m->vmm[0]);
   symFree(c, m->expertOut, m->wOut, m->vmm[1]);
   symFree(c, m->table, m->wTable, m->vmm[2]);
-  symFree(c, m->dup, m->wDup, m->vmm[3]);
+  symFree(c, m->grp, m->wGrp, m->vmm[3]);
+  symFree(c, m->partial, m->wPartial, m->vmm[4]);
   cudaFree(m->pos);
   cudaFree(m->route);
   cudaFree(m->expertOffsets);
+  cudaFree(m->lead);
   delete m;
   return flagcxSuccess;
 }

@@ -42,7 +42,8 @@ flagcxResult_t Tuner::init(flagcxComm *c) {
     static const struct { const char *n; int v; } names[] = {
         {"oneshot", FLAGCX_ALGO_ONESHOT}, {"twoshot", FLAGCX_ALGO_TWOSHOT},
         {"nvls_oneshot", FLAGCX_ALGO_NVLS_ONESHOT}, {"nvls_twoshot", FLAGCX_ALGO_NVLS_TWOSHOT},
-        {"push", FLAGCX_ALGO_PUSH}, {"pull", FLAGCX_ALGO_PULL}, {"nvls", FLAGCX_ALGO_NVLS}, {"ll", FLAGCX_ALGO_LL}, {"ring", FLAGCX_ALGO_RING}};
+        {"push", FLAGCX_ALGO_PUSH}, {"pull", FLAGCX_ALGO_PULL}, {"nvls", FLAGCX_ALGO_NVLS}, {"ll", FLAGCX_ALGO_LL}, {"ring", FLAGCX_ALGO_RING},
+        {"copy_engine", FLAGCX_ALGO_COPY_ENGINE}};
     for (auto &e : names)
       if (!strcasecmp(s, e.n)) forcedAlgo = e.v;
   }
@@ -226,6 +227,8 @@ std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, boo
       if (ctas > 1 && (size_t)ctas * 4096 > bytes) continue;
       out.push_back({a, ctas});
     }
+  // the copy engines move the data: no CTA count to choose
+  if (n > 1 && op == flagcxCommOpAllGather && registered && bytes >= (1u << 20)) out.push_back({FLAGCX_ALGO_COPY_ENGINE, 1});
   // the barrier-free path picks its own CTA count
   if (n > 1 && ((op == flagcxCommOpAllReduce && bytes <= llCap) ||
                 ((op == flagcxCommOpAllGather || op == flagcxCommOpReduceScatter || op == flagcxCommOpAlltoAll) &&

@@ -6,9 +6,12 @@
 // several experts of ONE rank want crosses NVLink once; the receiver makes the other
 // copies locally.  Counting the routing table and exchanging the counts that place the
 // rows happen inside the same kernel.
-// combine: every token gathers its top-k expert outputs from the ranks that hold
-// them, weights them in fp32 and stores one bf16 row: the all-to-all back and the
-// weighted sum are one pass, and the un-permutation is implicit.
+// combine: the mirror image.  The token's owner pushes the gate weights to the expert
+// ranks; each expert rank adds up, in fp32, the weighted outputs a token has on it (one
+// bf16 row per token and rank); the owner pulls those rows and sums them: one row per
+// (token, rank) crosses NVLink instead of one per (token, expert), the all-to-all back and
+// the weighted sum are one kernel, and the un-permutation is implicit.  With
+// preReduce = 0 the owner pulls every (token, expert) row and weights it itself.
 //
 // FlagCX offers only flagcxAlltoAllv for this (plugin/torch/flagcx/src/
 // backend_flagcx.cpp:926-993 in the FlagCX project); permutation and the weighted
@@ -37,12 +40,44 @@ __device__ __forceinline__ void warpCopyRow(char *dst, const char *src, int vecs
   for (; v < vecs; v += 32) st16(d + v, srcIsPeerWritten ? ldSys16(s + v) : s[v]);
 }
 
+// A group record (FLAGCX_MOE_MAX_TOPK ints written by a peer) as two 16-byte loads.
+__device__ __forceinline__ void loadGroup(const int *rec, int rows[FLAGCX_MOE_MAX_TOPK]) {
+  static_assert(FLAGCX_MOE_MAX_TOPK == 8, "a group record is two 16-byte vectors");
+  const uint4 lo = ldSys16(rec), hi = ldSys16(rec + 4);
+  rows[0] = (int)lo.x; rows[1] = (int)lo.y; rows[2] = (int)lo.z; rows[3] = (int)lo.w;
+  rows[4] = (int)hi.x; rows[5] = (int)hi.y; rows[6] = (int)hi.z; rows[7] = (int)hi.w;
+}
+
+// dst row = sum_k w[k] * rows[k] (null rows skipped), fp32 accumulation, one warp.
+__device__ __forceinline__ void weightedRowSum(const char *const rows[FLAGCX_MOE_MAX_TOPK], const float w[FLAGCX_MOE_MAX_TOPK],
+                                               uint4 *dst, int vecs, int lane, bool rowsArePeerWritten) {
+  for (int v = lane; v < vecs; v += 32) {
+    uint4 r[FLAGCX_MOE_MAX_TOPK];
+#pragma unroll
+    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
+      if (rows[k]) r[k] = rowsArePeerWritten ? ldSys16(rows[k] + (size_t)v * 16) : *(const uint4 *)(rows[k] + (size_t)v * 16);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
+      if (rows[k]) {
+        const __nv_bfloat16 *e = (const __nv_bfloat16 *)&r[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += w[k] * __bfloat162float(e[j]);
+      }
+    uint4 o;
+    __nv_bfloat16 *oe = (__nv_bfloat16 *)&o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(acc[j]);
+    st16(dst + v, o);
+  }
+}
+
 // The whole dispatch is this one kernel: histogram of the routing, exchange of the
 // counts, the copies, and the local fan-out of rows that several experts of one rank want.
 __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
   __shared__ int tot[FLAGCX_MOE_MAX_EXPERTS], base[FLAGCX_MOE_MAX_EXPERTS], before[FLAGCX_MOE_MAX_EXPERTS],
       mineCnt[FLAGCX_MOE_MAX_EXPERTS];
-  __shared__ int dupN[FLAGCX_MAX_RANKS];
+  __shared__ int grpN[FLAGCX_MAX_RANKS];
   const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
   const int t = threadIdx.x, nt = blockDim.x;
   // this CTA's tokens: a contiguous range, so that "how many earlier pairs chose expert e"
@@ -53,7 +88,7 @@ __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
   // 0. every CTA counts the whole routing table (a few dozen shared-memory atomics per
   // thread): no separate counting kernel, no global atomics, no memset
   for (int e = t; e < a.E; e += nt) tot[e] = before[e] = mineCnt[e] = 0;
-  if (t < FLAGCX_MAX_RANKS) dupN[t] = 0;
+  if (t < FLAGCX_MAX_RANKS) grpN[t] = 0;
   __syncthreads();
   for (int i = t; i < items; i += nt) {
     const int e = a.topkIdx[i];
@@ -108,12 +143,12 @@ __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
     }
   }
   // 3. one warp per token.  The first expert of each destination rank gets the row over
-  // NVLink, straight into its final place; for further experts on the same rank the
-  // receiver is left a (source row, destination row) record and copies locally.
+  // NVLink, straight into its final place; the destination is left a group record (all rows
+  // of that token there, leader first) from which it makes the other copies locally.
   const int warpsPerCta = nt >> 5, warp = t >> 5, lane = t & 31;
   const int vecs = a.H / 8; // 16-byte vectors per row
   const size_t rowBytes = (size_t)a.H * 2;
-  const int capPer = ((a.maxT + g - 1) / g) * (a.K > 1 ? a.K - 1 : 1);
+  const int capPer = ((a.maxT + g - 1) / g) * a.K;
   for (int tok = tlo + warp; tok < thi; tok += warpsPerCta) {
     int d = -1, row = 0;
     bool valid = false;
@@ -126,47 +161,56 @@ __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
         a.pos[i] = row; // any value >= 0 tells combine that the pair is real
         a.route[2 * i] = d;
         a.route[2 * i + 1] = row;
+        valid = (size_t)row < a.capacity; // rows past the capacity are reported by the receiver and dropped
       }
     }
     int firstLane = lane;
     for (int j = a.K - 1; j >= 0; --j) { // the smallest earlier lane with the same destination wins
-      const int dj = __shfl_sync(0xffffffffu, d, j);
-      if (a.dedup && j < lane && dj == d && d >= 0) firstLane = j;
+      const int dj = __shfl_sync(0xffffffffu, valid ? d : -1, j);
+      if (a.dedup && valid && j < lane && dj == d) firstLane = j;
     }
-    const bool isFirst = valid && firstLane == lane;
-    const int firstRow = __shfl_sync(0xffffffffu, row, firstLane);
-    if (valid && !isFirst && (size_t)row < a.capacity && (size_t)firstRow < a.capacity) {
-      const int idx = atomicAdd(&dupN[d], 1);
-      if (idx < capPer) {
-        int2 *rec = a.dupList[d] + (size_t)rank * a.dupRecordsPerSender + (size_t)b * capPer + idx;
-        *rec = make_int2(firstRow, row);
-      }
+    // lanes of one group find each other; the others (no pair, bad pair) are alone
+    const unsigned members = __match_any_sync(0xffffffffu, valid ? firstLane : 32 + lane);
+    const int member = __popc(members & ((1u << lane) - 1u)), groupSize = __popc(members);
+    const bool isFirst = valid && member == 0;
+    int idx = 0;
+    if (isFirst) idx = atomicAdd(&grpN[d], 1);
+    idx = __shfl_sync(0xffffffffu, idx, firstLane);
+    if (lane < a.K) a.lead[tok * a.K + lane] = isFirst ? 1 : 0;
+    if (valid && idx < capPer) {
+      int *rec = a.grpList[d] + ((size_t)rank * a.grpRecordsPerSender + (size_t)b * capPer + idx) * FLAGCX_MOE_MAX_TOPK;
+      rec[member] = row;
+      if (isFirst)
+        for (int j = groupSize; j < FLAGCX_MOE_MAX_TOPK; ++j) rec[j] = -1;
     }
     const char *src = (const char *)(a.x + (size_t)tok * a.H);
     for (int k = 0; k < a.K; ++k) {
       const int dk = __shfl_sync(0xffffffffu, d, k), rowk = __shfl_sync(0xffffffffu, row, k);
       const bool fk = __shfl_sync(0xffffffffu, isFirst ? 1 : 0, k) != 0;
-      if (fk && (size_t)rowk < a.capacity) // rows past the capacity are reported by the receiver
-        warpCopyRow(a.recv[dk] + (size_t)rowk * rowBytes, src, vecs, lane, false);
+      if (fk) warpCopyRow(a.recv[dk] + (size_t)rowk * rowBytes, src, vecs, lane, false);
     }
   }
   __syncthreads();
-  if (t < n) a.dupCount[t][(size_t)rank * FLAGCX_COLL_BARRIER_SLOTS + b] = dupN[t] < capPer ? dupN[t] : capPer;
+  if (t < n) a.grpCount[t][(size_t)rank * FLAGCX_COLL_BARRIER_SLOTS + b] = grpN[t] < capPer ? grpN[t] : capPer;
   if (!ctaBarrier(c, b)) return;
   // 4. the copies the senders' CTA b left to this rank: row to row inside my own buffer
   for (int q = 0; q < n; ++q) {
-    const int cnt = ldSysElem(a.dupCount[rank] + (size_t)q * FLAGCX_COLL_BARRIER_SLOTS + b);
-    const int2 *recs = a.dupList[rank] + (size_t)q * a.dupRecordsPerSender + (size_t)b * capPer;
+    const int cnt = ldSysElem(a.grpCount[rank] + (size_t)q * FLAGCX_COLL_BARRIER_SLOTS + b);
+    const int *recs = a.grpList[rank] + ((size_t)q * a.grpRecordsPerSender + (size_t)b * capPer) * FLAGCX_MOE_MAX_TOPK;
     for (int r = warp; r < cnt; r += warpsPerCta) {
-      const unsigned long long raw = fcxdev::ldRelaxedSys((const unsigned long long *)(recs + r));
-      const int srcRow = (int)(raw & 0xffffffffu), dstRow = (int)(raw >> 32);
-      if ((size_t)srcRow >= a.capacity || (size_t)dstRow >= a.capacity) continue;
-      warpCopyRow(a.recv[rank] + (size_t)dstRow * rowBytes, a.recv[rank] + (size_t)srcRow * rowBytes, vecs, lane, true);
+      int rows[FLAGCX_MOE_MAX_TOPK];
+      loadGroup(recs + (size_t)r * FLAGCX_MOE_MAX_TOPK, rows);
+      if ((size_t)rows[0] >= a.capacity) continue;
+#pragma unroll
+      for (int j = 1; j < FLAGCX_MOE_MAX_TOPK; ++j)
+        if (rows[j] >= 0 && (size_t)rows[j] < a.capacity)
+          warpCopyRow(a.recv[rank] + (size_t)rows[j] * rowBytes, a.recv[rank] + (size_t)rows[0] * rowBytes, vecs, lane, true);
     }
   }
 }
 
-__device__ void combineBody(const flagcxDevComm &c, const MoeArgs &a) {
+// Pull-everything combine: the token's owner reads each (token, expert) row and weights it.
+__device__ void combinePullBody(const flagcxDevComm &c, const MoeArgs &a) {
   const int b = blockIdx.x, g = gridDim.x;
   const int t = threadIdx.x, nt = blockDim.x;
   if (!ctaBarrier(c, b)) return; // every rank's expert outputs are complete
@@ -189,28 +233,71 @@ __device__ void combineBody(const flagcxDevComm &c, const MoeArgs &a) {
         w[k] = 0.f;
       }
     }
-    uint4 *dst = (uint4 *)(a.out + (size_t)tok * a.H);
-    for (int v = lane; v < vecs; v += 32) {
-      uint4 r[FLAGCX_MOE_MAX_TOPK];
-#pragma unroll
-      for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
-        if (rows[k]) r[k] = ldSys16(rows[k] + (size_t)v * 16);
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
-        if (rows[k]) {
-          const __nv_bfloat16 *e = (const __nv_bfloat16 *)&r[k];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += w[k] * __bfloat162float(e[j]);
-        }
-      uint4 o;
-      __nv_bfloat16 *oe = (__nv_bfloat16 *)&o;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(acc[j]);
-      dst[v] = o;
-    }
+    weightedRowSum(rows, w, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
   }
   ctaBarrier(c, b); // peers may overwrite their expert outputs only after everyone has read them
+}
+
+// Pre-reducing combine.  Everything is organised per CTA index, like the dispatch: the
+// groups that sender q's CTA b recorded here are reduced by this rank's CTA b and pulled
+// by q's CTA b, so the per-CTA barriers across ranks are all the ordering it needs.
+__device__ void combineReduceBody(const flagcxDevComm &c, const MoeArgs &a) {
+  const int b = blockIdx.x, g = gridDim.x, rank = c.rank, n = c.nRanks;
+  const int t = threadIdx.x, nt = blockDim.x;
+  const int warpsPerCta = nt >> 5, warp = t >> 5, lane = t & 31;
+  const int vecs = a.H / 8;
+  const size_t rowBytes = (size_t)a.H * 2;
+  const int tpc = (a.T + g - 1) / g; // the dispatch's token ranges
+  const int tlo = b * tpc < a.T ? b * tpc : a.T, thi = tlo + tpc < a.T ? tlo + tpc : a.T;
+  const int capPer = ((a.maxT + g - 1) / g) * a.K;
+  // 0. the gate weight of each of my pairs goes next to the row it weights
+  for (int i = tlo * a.K + t; i < thi * a.K; i += nt) {
+    const int d = a.route[2 * i], row = a.route[2 * i + 1];
+    if (a.pos[i] >= 0 && (size_t)row < a.capacity) a.wRow[d][row] = a.topkW[i];
+  }
+  if (!ctaBarrier(c, b)) return; // weights have landed; every rank's expert outputs are complete
+  // A. one row per group: the weighted sum of the group's expert outputs, all local reads
+  for (int q = 0; q < n; ++q) {
+    const int cnt = ldSysElem(a.grpCount[rank] + (size_t)q * FLAGCX_COLL_BARRIER_SLOTS + b);
+    const int *recs = a.grpList[rank] + ((size_t)q * a.grpRecordsPerSender + (size_t)b * capPer) * FLAGCX_MOE_MAX_TOPK;
+    for (int r = warp; r < cnt; r += warpsPerCta) {
+      int rowIdx[FLAGCX_MOE_MAX_TOPK];
+      loadGroup(recs + (size_t)r * FLAGCX_MOE_MAX_TOPK, rowIdx);
+      if ((size_t)rowIdx[0] >= a.capacity) continue;
+      const char *rows[FLAGCX_MOE_MAX_TOPK];
+      float w[FLAGCX_MOE_MAX_TOPK];
+#pragma unroll
+      for (int j = 0; j < FLAGCX_MOE_MAX_TOPK; ++j) {
+        const bool ok = rowIdx[j] >= 0 && (size_t)rowIdx[j] < a.capacity;
+        rows[j] = ok ? a.expertOut[rank] + (size_t)rowIdx[j] * rowBytes : nullptr;
+        w[j] = ok ? ldSysElem(a.wRow[rank] + rowIdx[j]) : 0.f;
+      }
+      weightedRowSum(rows, w, (uint4 *)(a.partial[rank] + (size_t)rowIdx[0] * rowBytes), vecs, lane, false);
+    }
+  }
+  if (!ctaBarrier(c, b)) return; // the partial rows of my tokens are complete on every rank
+  // B. each token adds up one row per rank it has experts on
+  for (int tok = tlo + warp; tok < thi; tok += warpsPerCta) {
+    const char *rows[FLAGCX_MOE_MAX_TOPK];
+    float w[FLAGCX_MOE_MAX_TOPK];
+#pragma unroll
+    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k) {
+      rows[k] = nullptr;
+      w[k] = 1.f;
+      if (k < a.K) {
+        const int i = tok * a.K + k;
+        const int d = a.route[2 * i], row = a.route[2 * i + 1];
+        if (a.pos[i] >= 0 && a.lead[i] && (size_t)row < a.capacity) rows[k] = a.partial[d] + (size_t)row * rowBytes;
+      }
+    }
+    weightedRowSum(rows, w, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
+  }
+  ctaBarrier(c, b); // weights and partial rows may be overwritten only after everyone has read them
+}
+
+__device__ void combineBody(const flagcxDevComm &c, const MoeArgs &a) {
+  if (a.preReduce) combineReduceBody(c, a);
+  else combinePullBody(c, a);
 }
 
 __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) moeDispatchKernel(const flagcxDevComm c, const MoeArgs a) {

@@ -21,15 +21,22 @@ struct MoeArgs {
   char *recv[FLAGCX_MAX_RANKS];      // recv[p]: rank p's receive buffer [capacity, H] bf16
   char *expertOut[FLAGCX_MAX_RANKS]; // expertOut[p]: rank p's expert outputs, same row order
   int *expertOffsets;      // local [EPR + 1]: row range of each local expert
-  // A token that goes to several experts of one rank crosses NVLink once: the first copy
-  // lands in its final row, and a (source row, destination row) record asks the receiver
-  // to make the other copies locally.  dupList[p] / dupCount[p]: rank p's record area
-  // [sender][CTA][dupCapPerCta] and count table [sender][CTA], as mapped here.
-  int2 *dupList[FLAGCX_MAX_RANKS];
-  int *dupCount[FLAGCX_MAX_RANKS];
-  int dupRecordsPerSender; // records reserved per sender in a rank's area
+  // A token that goes to several experts of one rank crosses NVLink once.  For every
+  // (token, destination rank) the sender leaves the destination a GROUP record: the rows
+  // that token occupies there, leader first (rows[0] got the data over NVLink; the
+  // receiver copies it to the others).  The combine uses the same records the other way:
+  // the expert rank adds up a group's weighted outputs locally and the token's owner pulls
+  // one row per group.  grpList[p] / grpCount[p]: rank p's record area
+  // [sender][CTA][records per CTA] and count table [sender][CTA], as mapped here.
+  int *grpList[FLAGCX_MAX_RANKS];   // records of FLAGCX_MOE_MAX_TOPK ints, -1 = unused
+  int *grpCount[FLAGCX_MAX_RANKS];
+  int grpRecordsPerSender; // records reserved per sender in a rank's area
   int maxT;                // largest token count any rank may pass (fixes the per-CTA share of that area)
-  int dedup;               // 0: every (token, expert) pair crosses NVLink on its own
+  int dedup;               // 0: every (token, expert) pair crosses NVLink on its own (groups of one)
+  int preReduce;           // combine: 1 = expert ranks pre-reduce each group, 0 = owners pull every pair
+  int *lead;               // local [T*K]: 1 where the pair leads its group
+  float *wRow[FLAGCX_MAX_RANKS];     // wRow[p]: rank p's gate weight per received row (pushed by the combine)
+  char *partial[FLAGCX_MAX_RANKS];   // partial[p]: rank p's pre-reduced rows, indexed by the group's leader row
   int T, H, K, E, EPR;
   size_t capacity;         // rows in recv / expertOut
 };

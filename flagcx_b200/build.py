@@ -24,7 +24,9 @@ def build_devtest(verbose: bool = False) -> str:
     library next to their source; tests/test_gpu_device_api.py loads it."""
     src = os.path.join(ROOT, "csrc", "tests", "device_api_kernels.cu")
     lib = os.path.join(ROOT, "csrc", "tests", "libflagcx_devtest.so")
-    if os.path.exists(lib) and os.path.getmtime(lib) >= os.path.getmtime(src):
+    inc = os.path.join(ROOT, "csrc", "include")
+    deps = [src] + [os.path.join(inc, f) for f in os.listdir(inc)]
+    if os.path.exists(lib) and os.path.getmtime(lib) >= max(os.path.getmtime(d) for d in deps):
         return lib
     cmd = ["/usr/local/cuda/bin/nvcc", "-std=c++17", "-O2", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
            "-shared", "-Xcompiler", "-fPIC", "-cudart", "shared", "-I" + os.path.join(ROOT, "csrc", "include"), src, "-o", lib]

@@ -38,7 +38,8 @@ OP_SEND, OP_RECV, OP_BROADCAST, OP_GATHER, OP_SCATTER, OP_REDUCE, OP_ALLREDUCE, 
     OP_ALLGATHER, OP_REDUCESCATTER, OP_ALLTOALL, OP_ALLTOALLV = range(11)
 
 ALGO_AUTO = -1
-ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS_ONESHOT, ALGO_NVLS_TWOSHOT, ALGO_PUSH, ALGO_PULL, ALGO_NVLS, ALGO_LL, ALGO_RING = range(9)
+(ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS_ONESHOT, ALGO_NVLS_TWOSHOT, ALGO_PUSH, ALGO_PULL, ALGO_NVLS, ALGO_LL, ALGO_RING,
+ ALGO_COPY_ENGINE) = range(10)
 
 WIN_DEFAULT = 0
 WIN_COLL_SYMMETRIC = 1

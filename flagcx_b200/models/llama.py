@@ -9,6 +9,7 @@ rotary embedding, SwiGLU and the loss are this package's fused kernels.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, List, Sequence, Tuple
 
@@ -72,6 +73,23 @@ def _make_layer_fn(cfg: LlamaConfig):
     def layer(params, x):
         attn_norm, wqkv, wo, ffn_norm, w13, w2 = params
         T = x.shape[0]
+        h, skip = ops.rmsnorm_branch(x, attn_norm, cfg.eps)
+        qkv = ops.rope_fused_qkv(ops.linear(h, wqkv), nh, nkv, hd, cfg.rope_theta)
+        q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)  # views: attention reads them strided
+        q, k, v = q.view(T, nh, hd), k.view(T, nkv, hd), v.view(T, nkv, hd)
+        a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
+                                           v.transpose(0, 1).unsqueeze(0), is_causal=True, enable_gqa=True)
+        a = a.squeeze(0).transpose(0, 1).reshape(T, nh * hd)
+        x = ops.linear(a, wo, residual=skip)
+        h, skip = ops.rmsnorm_branch(x, ffn_norm, cfg.eps)
+        x = ops.linear(ops.swiglu(ops.linear(h, w13)), w2, residual=skip)
+        return x
+
+    def layer_unfused(params, x):
+        """The same block from one kernel per operation (separate q / k rotations on copies,
+        residual adds as their own kernels): the comparison arm of FLAGCX_MODEL_FUSED=0."""
+        attn_norm, wqkv, wo, ffn_norm, w13, w2 = params
+        T = x.shape[0]
         h = ops.rmsnorm(x, attn_norm, cfg.eps)
         qkv = ops.linear(h, wqkv)
         q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
@@ -86,6 +104,8 @@ def _make_layer_fn(cfg: LlamaConfig):
         x = x + ops.linear(ops.swiglu(ops.linear(h, w13)), w2)
         return x
 
+    if os.environ.get("FLAGCX_MODEL_FUSED", "1") == "0":
+        return layer_unfused
     return layer
 
 

@@ -60,6 +60,35 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.T
     return _RMSNorm.apply(x.contiguous(), weight, eps)
 
 
+class _RMSNormBranch(torch.autograd.Function):
+    """The pre-norm of a residual block: returns (norm(x), x).  The second output is x itself,
+    to be used as the block's skip connection; routing it through this function lets the
+    backward add the skip connection's gradient to the norm's input gradient inside the
+    RMSNorm backward kernel, where autograd would otherwise launch an add over [T, H]."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        y, rstd = ext().rmsnorm_fwd(x, weight, eps)
+        _count()
+        ctx.save_for_backward(x, weight, rstd)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g, g_skip):
+        x, weight, rstd = ctx.saved_tensors
+        if g is None:  # only the skip connection was used
+            return g_skip, None, None
+        add = g_skip.contiguous() if g_skip is not None else None
+        dx, dw = ext().rmsnorm_bwd(g.contiguous(), x, weight, rstd, add)
+        _count()
+        return dx, dw, None
+
+
+def rmsnorm_branch(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5):
+    """(rmsnorm(x), x): see _RMSNormBranch.  Use the second value for the residual add."""
+    return _RMSNormBranch.apply(x.contiguous(), weight, eps)
+
+
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, theta):
@@ -82,6 +111,28 @@ def rope(x: torch.Tensor, theta: float = 500000.0) -> torch.Tensor:
     return _Rope.apply(x, theta)
 
 
+class _RopeFusedQkv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, rope_heads, total_heads, head_dim, theta):
+        ctx.shape = (rope_heads, total_heads, head_dim, theta)
+        _count()
+        return ext().rope_fused_qkv(qkv, rope_heads, total_heads, head_dim, theta, False)
+
+    @staticmethod
+    def backward(ctx, g):
+        rope_heads, total_heads, head_dim, theta = ctx.shape
+        _count()
+        return ext().rope_fused_qkv(g.contiguous(), rope_heads, total_heads, head_dim, theta, True), None, None, None, None
+
+
+def rope_fused_qkv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, theta: float = 500000.0) -> torch.Tensor:
+    """qkv: [tokens, (n_heads + 2 * n_kv_heads) * head_dim] as the fused projection leaves it
+    (queries, keys, values side by side).  Rotates the query and key heads (token t at
+    position t) and copies the value heads, in one pass; q, k and v are then views of the
+    result and no per-tensor copy is needed before attention."""
+    return _RopeFusedQkv.apply(qkv.contiguous(), n_heads + n_kv_heads, n_heads + 2 * n_kv_heads, head_dim, theta)
+
+
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ab):
@@ -102,17 +153,25 @@ def swiglu(ab: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(ab)
 
 
+def _mm_residual(x, w, residual):
+    # cuBLAS adds the residual in the GEMM's epilogue (beta = 1): no separate add kernel
+    y = torch.addmm(residual.reshape(-1, residual.shape[-1]), x.reshape(-1, x.shape[-1]), w.t())
+    return y.view(*x.shape[:-1], w.shape[0])
+
+
 class _LinearInto(torch.autograd.Function):
-    """y = x @ w.T whose weight gradient is written by the GEMM itself into a buffer the
-    caller owns (a slice of a flat gradient buffer), instead of into a fresh tensor that
-    would then be copied there.  `sink` is (destination [out, in], callback run once the
-    GEMM is queued); the weight's .grad stays None."""
+    """y = x @ w.T (+ residual) whose weight gradient is written by the GEMM itself into a
+    buffer the caller owns (a slice of a flat gradient buffer), instead of into a fresh
+    tensor that would then be copied there.  `sink` is (destination [out, in], callback run
+    once the GEMM is queued); the weight's .grad stays None."""
 
     @staticmethod
-    def forward(ctx, x, w, sink):
+    def forward(ctx, x, w, sink, residual):
         ctx.save_for_backward(x, w)
         ctx.sink = sink
-        return torch.nn.functional.linear(x, w)
+        if residual is None:
+            return torch.nn.functional.linear(x, w)
+        return _mm_residual(x, w, residual)
 
     @staticmethod
     def backward(ctx, g):
@@ -121,15 +180,35 @@ class _LinearInto(torch.autograd.Function):
         dx = g.matmul(w) if ctx.needs_input_grad[0] else None
         torch.mm(g.reshape(-1, g.shape[-1]).t(), x.reshape(-1, x.shape[-1]), out=dst)
         done()
-        return dx, None, None
+        return dx, None, None, (g if ctx.needs_input_grad[3] else None)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """F.linear; if the weight carries a `_grad_sink` its gradient goes straight there."""
+class _LinearResidual(torch.autograd.Function):
+    """y = x @ w.T + residual with the add in the GEMM epilogue; the residual's gradient is
+    the incoming gradient itself (no kernel)."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual):
+        ctx.save_for_backward(x, w)
+        return _mm_residual(x, w, residual)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        dx = g.matmul(w) if ctx.needs_input_grad[0] else None
+        dw = g.reshape(-1, g.shape[-1]).t().mm(x.reshape(-1, x.shape[-1])) if ctx.needs_input_grad[1] else None
+        return dx, dw, (g if ctx.needs_input_grad[2] else None)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """F.linear, optionally with `residual` (same shape as the result) added in the GEMM's
+    epilogue; if the weight carries a `_grad_sink` its gradient goes straight there."""
     sink = getattr(w, "_grad_sink", None)
     if sink is None:
-        return torch.nn.functional.linear(x, w)
-    return _LinearInto.apply(x, w, sink)
+        if residual is None:
+            return torch.nn.functional.linear(x, w)
+        return _LinearResidual.apply(x, w, residual)
+    return _LinearInto.apply(x, w, sink, residual)
 
 
 _unit_grad_checked = False

@@ -49,6 +49,11 @@ class ShardedModel:
         # the choice to the communicator's tuner
         self.comm_ctas = comm_ctas if comm_ctas is not None else int(os.environ.get("FLAGCX_FSDP_CTAS", "24"))
         self.comm_launches = 0
+        # How the parameter all-gather moves its data: "push" = the NVLink kernel (comm_ctas
+        # CTAs store into the peers' buffers), "copy_engine" = DMA copy engines between two
+        # one-CTA barrier kernels, which leaves every SM to the GEMMs it runs beside.
+        self.gather_algo = {"push": capi.ALGO_PUSH, "copy_engine": capi.ALGO_COPY_ENGINE}[
+            os.environ.get("FLAGCX_FSDP_ALLGATHER", "push")]
         # AdamW of a unit runs on its own stream as soon as that unit's gradients are
         # reduced, underneath the backward pass of the units before it (it is bound by
         # memory bandwidth, the backward GEMMs by the tensor cores), instead of after the
@@ -175,7 +180,7 @@ class ShardedModel:
         if self.compute_done[b] is not None:
             cs.wait_event(self.compute_done[b])  # previous occupant is no longer needed
         self.comm.all_gather(self.shard[u], self.param_buf[b], self.shard_numel[u], capi.BFLOAT16, stream=cs,
-                             algo=capi.ALGO_PUSH, nctas=self.comm_ctas)
+                             algo=self.gather_algo, nctas=self.comm_ctas)
         self.comm_launches += 1
         ev = torch.cuda.Event()
         ev.record(cs)

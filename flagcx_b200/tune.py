@@ -22,7 +22,7 @@ from flagcx_b200.utils.dist import init_world
 
 OPS = {"allreduce": capi.OP_ALLREDUCE, "allgather": capi.OP_ALLGATHER, "reducescatter": capi.OP_REDUCESCATTER,
        "alltoall": capi.OP_ALLTOALL}
-ALGO_NAMES = ["oneshot", "twoshot", "nvls_oneshot", "nvls_twoshot", "push", "pull", "nvls", "ll", "ring"]
+ALGO_NAMES = ["oneshot", "twoshot", "nvls_oneshot", "nvls_twoshot", "push", "pull", "nvls", "ll", "ring", "copy_engine"]
 
 
 def parse_size(s: str) -> int:

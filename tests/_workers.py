@@ -45,7 +45,7 @@ def rel_err(got, ref):
 
 
 def host_collectives(rank, n, uid, count, dtype_code):
-    """BASELINE config 1: allreduce / allgather / reducescatter / alltoall / send-recv
+    """Host-buffer collectives: allreduce / allgather / reducescatter / alltoall / send-recv
     on host buffers, checked against numpy."""
     comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
     assert comm.rank == rank and comm.nranks == n
@@ -441,6 +441,51 @@ def gpu_nvls_collectives(rank, n, uid, count):
         # nobody leaves while a peer's memory is still bound to the multicast object
         for b in bufs:
             b.free()
+        comm.destroy()
+    return worst
+
+
+def gpu_copy_engine_allgather(rank, n, uid, count, rounds):
+    """All-gather into a window with the data moved by the copy engines (two one-CTA barrier
+    kernels around n peer copies): exact results over several rounds that reuse the same
+    output buffer with changing contents, out of place and in place, while one rank is
+    slowed down by extra work in its stream."""
+    import torch
+    from flagcx_b200.utils.symm import SymmetricBuffer
+    torch.cuda.set_device(rank)
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    worst = {}
+    buf = SymmetricBuffer(comm, count * n * 2)
+    out = buf.view(torch.bfloat16, count * n)
+    src = torch.empty(count, dtype=torch.bfloat16, device="cuda")
+    ballast = torch.randn(2048, 2048, device="cuda")
+    try:
+        for it in range(rounds):
+            if rank == it % n:  # a straggler: its peers reach the collective long before it
+                for _ in range(20):
+                    ballast = (ballast @ ballast).clamp_(-1, 1)
+            in_place = it % 2 == 1
+            val = lambda r: float((r + 1) * 8 + it % 7)
+            if in_place:
+                mine = out[rank * count:(rank + 1) * count]
+                mine.fill_(val(rank))
+            else:
+                mine = src
+                mine.fill_(val(rank))
+            comm.all_gather(mine, out, count, capi.BFLOAT16, algo=capi.ALGO_COPY_ENGINE)
+            if comm.stats(capi.OP_ALLGATHER).lastAlgo != capi.ALGO_COPY_ENGINE:
+                worst["fell_back"] = 2.0
+            got = out.view(n, count).float()
+            want = torch.tensor([val(r) for r in range(n)], device="cuda")[:, None].expand(n, count)
+            if not torch.equal(got, want):
+                worst[f"round{it}"] = 2.0
+        torch.cuda.synchronize()
+        if comm.async_error() != 0:
+            worst["device_error"] = 2.0
+    finally:
+        torch.cuda.synchronize()
+        comm.barrier()
+        buf.free()
         comm.destroy()
     return worst
 

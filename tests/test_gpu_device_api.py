@@ -18,10 +18,8 @@ LIB = os.path.join(ROOT, "csrc", "tests", "libflagcx_devtest.so")
 
 
 def _testlib():
-    if not os.path.exists(LIB) or os.path.getmtime(LIB) < os.path.getmtime(SRC):
-        subprocess.check_call(["/usr/local/cuda/bin/nvcc", "-std=c++17", "-O2", "-lineinfo", "-gencode",
-                               "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-cudart", "shared",
-                               "-I" + os.path.join(ROOT, "csrc", "include"), SRC, "-o", LIB])
+    from flagcx_b200.build import build_devtest
+    assert build_devtest() == LIB  # rebuilt when its source or a device header is newer
     lib = C.CDLL(LIB)
     lib.fcxDevTestLaunch.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     return lib

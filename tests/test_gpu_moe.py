@@ -18,8 +18,13 @@ def _sorted_rows(rows: torch.Tensor) -> torch.Tensor:
     return bits[order]
 
 
-@pytest.mark.parametrize("n,T,H,E,K", [(2, 33, 128, 8, 2), (4, 64, 256, 16, 4), (8, 96, 512, 64, 8)])
-def test_dispatch_groups_rows_by_expert_and_combine_weights_them(n, T, H, E, K):
+# dedup: a token crosses NVLink once per destination rank (1) or once per expert (0);
+# reduce: the expert rank adds up a token's weighted outputs (1) or the owner pulls every row (0)
+@pytest.mark.parametrize("dedup,reduce", [(1, 1), (1, 0), (0, 1), (0, 0)])
+@pytest.mark.parametrize("n,T,H,E,K", [(2, 33, 128, 8, 2), (4, 64, 256, 16, 4), (8, 96, 512, 64, 8), (2, 70, 128, 4, 4)])
+def test_dispatch_groups_rows_by_expert_and_combine_weights_them(n, T, H, E, K, dedup, reduce, monkeypatch):
+    monkeypatch.setenv("FLAGCX_MOE_DEDUP", str(dedup))
+    monkeypatch.setenv("FLAGCX_MOE_COMBINE_REDUCE", str(reduce))
     comms = capi.Comm.emu_world(n, 0)
     try:
         epr = E // n

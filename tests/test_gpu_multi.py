@@ -61,6 +61,15 @@ def test_nvls_multimem_kernels():
 
 
 @needs2
+def test_copy_engine_allgather_with_a_straggler():
+    n = 8 if ngpus() >= 8 else 4 if ngpus() >= 4 else 2
+    res = run_ranks(n, "gpu_copy_engine_allgather", 1 << 20, 12, timeout=300)
+    for rank, worst in res.items():
+        bad = {k: v for k, v in worst.items() if v > 1.0}
+        assert not bad, (rank, bad)
+
+
+@needs2
 def test_two_level_route_when_one_machine_poses_as_several_nodes():
     """FLAGCX_HOSTID splits the machine: 2 nodes x 2 GPUs where there are four, else 2 x 1."""
     per_node = 2 if ngpus() >= 4 else 1
