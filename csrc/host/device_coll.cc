@@ -550,6 +550,43 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_PULL; // not eligible above
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpReduceScatter, count * es * n, algo, nCtas);
+  if (algo == FLAGCX_ALGO_COPY_ENGINE) {
+    if (n > 1 && !c->emu && count > 0) {
+      // The transport runs on the copy engines: every rank copies block p of its input into
+      // slot `rank` of peer p's staging area (n-1 peer copies between two one-CTA barrier
+      // kernels), then a kernel without any barrier reduces the n blocks that are now all
+      // in local memory.  No SM moves a byte over NVLink, and no buffer has to be visible
+      // to the peers.
+      const size_t S = c->layout.stagingBytes;
+      const size_t chunk = S / n / es / 16 * 16; // elements per slot
+      char *stage[FLAGCX_MAX_RANKS];
+      for (int p = 0; p < n; ++p) stage[p] = (char *)c->internalWin->peer[p] + c->layout.stagingOff;
+      const int me = c->rank;
+      for (size_t off = 0; off < count; off += chunk) {
+        const size_t cnt = std::min(chunk, count - off);
+        FCXCHECK(deviceBarrier(c, stream)); // the slots are free: every rank has finished the reduce before
+        for (int i = 1; i < n; ++i) {
+          const int p = (me + i) % n;
+          FCX_CUDACHECK(cudaMemcpyAsync(stage[p] + (size_t)me * chunk * es, (const char *)rq.send + ((size_t)p * count + off) * es,
+                                        cnt * es, cudaMemcpyDeviceToDevice, stream));
+        }
+        FCXCHECK(deviceBarrier(c, stream)); // every rank's copies have completed
+        CollArgs r = a;
+        r.kind = kReduceScatter;
+        r.count = cnt;
+        r.inStride = 0; // in[q] points at the block itself
+        r.flags = 0;
+        for (int q = 0; q < n; ++q)
+          r.in[q] = q == me ? (const char *)rq.send + ((size_t)me * count + off) * es : stage[me] + (size_t)q * chunk * es;
+        setOut(c, r, BufView(), rq.recv, off * oes);
+        r.residual = rq.residual ? (const char *)rq.residual + off * oes : nullptr;
+        setExtents(r, cnt * es, cnt * oes);
+        FCXCHECK(launch(c, kFamReduce, r, nCtas, stream));
+      }
+      return flagcxSuccess;
+    }
+    algo = FLAGCX_ALGO_PULL;
+  }
   if (algo == FLAGCX_ALGO_RING && n > 1 && a.outMode == kOutSame && !a.residual) {
     // neighbours only ever write into each other's scratch: no buffer needs to be visible
     a.kind = kReduceScatterRing;
@@ -714,7 +751,7 @@ flagcxResult_t copyCollective(flagcxComm *c, const DeviceCollRequest &rq, cudaSt
   if (algo == FLAGCX_ALGO_RING) algo = FLAGCX_ALGO_PUSH;
   if (algo == FLAGCX_ALGO_PUSH && !(outVis && pushKind >= 0)) algo = FLAGCX_ALGO_PULL;
   if (algo == FLAGCX_ALGO_PULL && !inVis && outVis && pushKind >= 0) algo = FLAGCX_ALGO_PUSH; // avoids staging
-  if (algo != FLAGCX_ALGO_PUSH && algo != FLAGCX_ALGO_NVLS) algo = FLAGCX_ALGO_PULL;
+  if (algo != FLAGCX_ALGO_PUSH && algo != FLAGCX_ALGO_NVLS && !ceWanted) algo = FLAGCX_ALGO_PULL;
   const int nCtas = pickCtas(c, rq, ch);
   note(c, rq.op, std::max(sendBytes, recvBytes), algo, nCtas);
 

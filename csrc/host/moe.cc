@@ -99,7 +99,7 @@ cudaError_t emuCombine(const LaunchCtx &lc, const void *d) {
 }
 
 int moeCtas(flagcxComm *c) {
-  int64_t v = readParam("MOE_CTAS", 64);
+  int64_t v = readParam("MOE_CTAS", 128); // CTAs of 256 threads
   return (int)std::max<int64_t>(1, std::min<int64_t>(v, FLAGCX_COLL_BARRIER_SLOTS));
 }
 

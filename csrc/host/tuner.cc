@@ -229,6 +229,10 @@ std::vector<Candidate> candidatesFor(flagcxCommOp_t op, size_t bytes, int n, boo
     }
   // the copy engines move the data: no CTA count to choose
   if (n > 1 && op == flagcxCommOpAllGather && registered && bytes >= (1u << 20)) out.push_back({FLAGCX_ALGO_COPY_ENGINE, 1});
+  // reduce-scatter: copy engines for the transport, then a local reduce with `ctas` CTAs
+  if (n > 1 && op == flagcxCommOpReduceScatter && bytes >= (1u << 20))
+    for (int ctas : {8, 16, 32})
+      if (ctas <= maxCtas) out.push_back({FLAGCX_ALGO_COPY_ENGINE, ctas});
   // the barrier-free path picks its own CTA count
   if (n > 1 && ((op == flagcxCommOpAllReduce && bytes <= llCap) ||
                 ((op == flagcxCommOpAllGather || op == flagcxCommOpReduceScatter || op == flagcxCommOpAlltoAll) &&

@@ -24,8 +24,9 @@ typedef enum {
   FLAGCX_ALGO_NVLS = 6,         /* reduce-scatter: multimem.ld_reduce; allgather: multimem.st */
   FLAGCX_ALGO_LL = 7,           /* allreduce/allgather of small messages: data+flag stores, no barrier */
   FLAGCX_ALGO_RING = 8,         /* allreduce/reduce-scatter/allgather in n-1 neighbour-to-neighbour steps */
-  FLAGCX_ALGO_COPY_ENGINE = 9,  /* allgather into a window: the data moves on the DMA copy engines, between two
-                                   one-CTA barrier kernels; no SM does any copying */
+  FLAGCX_ALGO_COPY_ENGINE = 9,  /* the data crosses NVLink on the DMA copy engines, between two one-CTA barrier
+                                   kernels: allgather into a window; reduce-scatter of any buffers (peer copies
+                                   into the staging area, then a reduce over local memory only) */
   FLAGCX_ALGO_COUNT = 10
 } flagcxAlgo_t;
 

@@ -26,6 +26,10 @@
 namespace fcx {
 namespace {
 
+// CTAs of 8 warps: the combine keeps eight 16-byte loads per lane in flight and wants the
+// registers for them; the host launches twice as many CTAs as it would of the 512-thread kind.
+constexpr int kMoeThreads = 256;
+
 // One warp copies one row (H bf16) with 16-byte accesses, four loads in flight per lane.
 __device__ __forceinline__ void warpCopyRow(char *dst, const char *src, int vecs, int lane, bool srcIsPeerWritten) {
   const uint4 *s = (const uint4 *)src;
@@ -48,27 +52,63 @@ __device__ __forceinline__ void loadGroup(const int *rec, int rows[FLAGCX_MOE_MA
   rows[4] = (int)hi.x; rows[5] = (int)hi.y; rows[6] = (int)hi.z; rows[7] = (int)hi.w;
 }
 
-// dst row = sum_k w[k] * rows[k] (null rows skipped), fp32 accumulation, one warp.
-__device__ __forceinline__ void weightedRowSum(const char *const rows[FLAGCX_MOE_MAX_TOPK], const float w[FLAGCX_MOE_MAX_TOPK],
-                                               uint4 *dst, int vecs, int lane, bool rowsArePeerWritten) {
-  for (int v = lane; v < vecs; v += 32) {
-    uint4 r[FLAGCX_MOE_MAX_TOPK];
+// dst row = sum over M rows of w[j] * rows[j], fp32 accumulation, one warp.  U vectors of
+// every row are loaded before any is used, so a lane has M*U 16-byte loads in flight.
+template <int M, int U>
+__device__ __forceinline__ void rowSumFixed(const char *const *rows, const float *w, uint4 *dst, int vecs, int lane,
+                                            bool peerWritten) {
+  for (int v0 = lane; v0 < vecs; v0 += 32 * U) {
+    uint4 r[U][M];
 #pragma unroll
-    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
-      if (rows[k]) r[k] = rowsArePeerWritten ? ldSys16(rows[k] + (size_t)v * 16) : *(const uint4 *)(rows[k] + (size_t)v * 16);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < vecs) {
 #pragma unroll
-    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
-      if (rows[k]) {
-        const __nv_bfloat16 *e = (const __nv_bfloat16 *)&r[k];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += w[k] * __bfloat162float(e[j]);
+        for (int j = 0; j < M; ++j)
+          r[u][j] = peerWritten ? ldSys16(rows[j] + (size_t)v * 16) : *(const uint4 *)(rows[j] + (size_t)v * 16);
       }
-    uint4 o;
-    __nv_bfloat16 *oe = (__nv_bfloat16 *)&o;
+    }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(acc[j]);
-    st16(dst + v, o);
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < vecs) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < M; ++j) {
+          const __nv_bfloat16 *e = (const __nv_bfloat16 *)&r[u][j];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += w[j] * __bfloat162float(e[i]);
+        }
+        uint4 o;
+        __nv_bfloat16 *oe = (__nv_bfloat16 *)&o;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) oe[i] = __float2bfloat16_rn(acc[i]);
+        st16(dst + v, o);
+      }
+    }
+  }
+}
+
+// dst row = sum of the first m rows, weighted (m = 0: zeros).  Few rows mean more vectors
+// per row in flight: 8 loads per lane either way.  m is the same for all lanes of the warp.
+__device__ __forceinline__ void weightedRowSum(const char *rows[FLAGCX_MOE_MAX_TOPK], float w[FLAGCX_MOE_MAX_TOPK], int m,
+                                               uint4 *dst, int vecs, int lane, bool rowsArePeerWritten) {
+  if (m == 0) {
+    for (int v = lane; v < vecs; v += 32) st16(dst + v, make_uint4(0, 0, 0, 0));
+  } else if (m == 1) {
+    rowSumFixed<1, 8>(rows, w, dst, vecs, lane, rowsArePeerWritten);
+  } else if (m == 2) {
+    rowSumFixed<2, 4>(rows, w, dst, vecs, lane, rowsArePeerWritten);
+  } else if (m <= 4) {
+#pragma unroll
+    for (int j = 2; j < 4; ++j)
+      if (j >= m) { rows[j] = rows[0]; w[j] = 0.f; } // pad with a weightless repeat of a valid row
+    rowSumFixed<4, 2>(rows, w, dst, vecs, lane, rowsArePeerWritten);
+  } else {
+#pragma unroll
+    for (int j = 4; j < FLAGCX_MOE_MAX_TOPK; ++j)
+      if (j >= m) { rows[j] = rows[0]; w[j] = 0.f; }
+    rowSumFixed<8, 1>(rows, w, dst, vecs, lane, rowsArePeerWritten);
   }
 }
 
@@ -176,7 +216,11 @@ __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
     int idx = 0;
     if (isFirst) idx = atomicAdd(&grpN[d], 1);
     idx = __shfl_sync(0xffffffffu, idx, firstLane);
-    if (lane < a.K) a.lead[tok * a.K + lane] = isFirst ? 1 : 0;
+    // the token's groups, packed: entry j = pair index of the j-th leader, -1 after the last
+    const unsigned leaders = __ballot_sync(0xffffffffu, isFirst);
+    if (lane < a.K) a.lead[tok * a.K + lane] = -1;
+    __syncwarp();
+    if (isFirst) a.lead[tok * a.K + __popc(leaders & ((1u << lane) - 1u))] = lane;
     if (valid && idx < capPer) {
       int *rec = a.grpList[d] + ((size_t)rank * a.grpRecordsPerSender + (size_t)b * capPer + idx) * FLAGCX_MOE_MAX_TOPK;
       rec[member] = row;
@@ -220,20 +264,26 @@ __device__ void combinePullBody(const flagcxDevComm &c, const MoeArgs &a) {
   for (int tok = b * warpsPerCta + warp; tok < a.T; tok += g * warpsPerCta) {
     const char *rows[FLAGCX_MOE_MAX_TOPK];
     float w[FLAGCX_MOE_MAX_TOPK];
+    const char *anyRow = nullptr;
 #pragma unroll
     for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k) {
+      rows[k] = nullptr;
+      w[k] = 0.f;
       if (k < a.K) {
         int i = tok * a.K + k;
         int d = a.route[2 * i], row = a.route[2 * i + 1];
-        bool ok = a.pos[i] >= 0 && (size_t)row < a.capacity;
-        rows[k] = ok ? a.expertOut[d] + (size_t)row * rowBytes : nullptr;
-        w[k] = ok ? a.topkW[i] : 0.f;
-      } else {
-        rows[k] = nullptr;
-        w[k] = 0.f;
+        if (a.pos[i] >= 0 && (size_t)row < a.capacity) {
+          rows[k] = a.expertOut[d] + (size_t)row * rowBytes;
+          w[k] = a.topkW[i];
+          anyRow = rows[k];
+        }
       }
     }
-    weightedRowSum(rows, w, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
+    // a pair that does not exist (bad expert id, row past the capacity) reads a valid row with weight 0
+#pragma unroll
+    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
+      if (!rows[k]) rows[k] = anyRow;
+    weightedRowSum(rows, w, anyRow ? a.K : 0, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
   }
   ctaBarrier(c, b); // peers may overwrite their expert outputs only after everyone has read them
 }
@@ -266,13 +316,15 @@ __device__ void combineReduceBody(const flagcxDevComm &c, const MoeArgs &a) {
       if ((size_t)rowIdx[0] >= a.capacity) continue;
       const char *rows[FLAGCX_MOE_MAX_TOPK];
       float w[FLAGCX_MOE_MAX_TOPK];
+      int m = 0; // the record is packed: valid rows first
 #pragma unroll
       for (int j = 0; j < FLAGCX_MOE_MAX_TOPK; ++j) {
-        const bool ok = rowIdx[j] >= 0 && (size_t)rowIdx[j] < a.capacity;
+        const bool ok = j == m && rowIdx[j] >= 0 && (size_t)rowIdx[j] < a.capacity;
         rows[j] = ok ? a.expertOut[rank] + (size_t)rowIdx[j] * rowBytes : nullptr;
         w[j] = ok ? ldSysElem(a.wRow[rank] + rowIdx[j]) : 0.f;
+        m += ok ? 1 : 0;
       }
-      weightedRowSum(rows, w, (uint4 *)(a.partial[rank] + (size_t)rowIdx[0] * rowBytes), vecs, lane, false);
+      weightedRowSum(rows, w, m, (uint4 *)(a.partial[rank] + (size_t)rowIdx[0] * rowBytes), vecs, lane, false);
     }
   }
   if (!ctaBarrier(c, b)) return; // the partial rows of my tokens are complete on every rank
@@ -280,17 +332,21 @@ __device__ void combineReduceBody(const flagcxDevComm &c, const MoeArgs &a) {
   for (int tok = tlo + warp; tok < thi; tok += warpsPerCta) {
     const char *rows[FLAGCX_MOE_MAX_TOPK];
     float w[FLAGCX_MOE_MAX_TOPK];
+    int m = 0;
 #pragma unroll
-    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k) {
-      rows[k] = nullptr;
-      w[k] = 1.f;
-      if (k < a.K) {
-        const int i = tok * a.K + k;
-        const int d = a.route[2 * i], row = a.route[2 * i + 1];
-        if (a.pos[i] >= 0 && a.lead[i] && (size_t)row < a.capacity) rows[k] = a.partial[d] + (size_t)row * rowBytes;
+    for (int j = 0; j < FLAGCX_MOE_MAX_TOPK; ++j) {
+      rows[j] = nullptr;
+      w[j] = 1.f;
+      if (j < a.K) {
+        const int k = a.lead[tok * a.K + j]; // pair index of this token's j-th group, -1 after the last
+        if (j == m && k >= 0) {
+          const int i = tok * a.K + k;
+          rows[j] = a.partial[a.route[2 * i]] + (size_t)a.route[2 * i + 1] * rowBytes;
+          ++m;
+        }
       }
     }
-    weightedRowSum(rows, w, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
+    weightedRowSum(rows, w, m, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
   }
   ctaBarrier(c, b); // weights and partial rows may be overwritten only after everyone has read them
 }
@@ -300,17 +356,17 @@ __device__ void combineBody(const flagcxDevComm &c, const MoeArgs &a) {
   else combinePullBody(c, a);
 }
 
-__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) moeDispatchKernel(const flagcxDevComm c, const MoeArgs a) {
+__global__ void __launch_bounds__(kMoeThreads) moeDispatchKernel(const flagcxDevComm c, const MoeArgs a) {
   dispatchBody(c, a);
 }
-__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+__global__ void __launch_bounds__(kMoeThreads)
     moeDispatchKernelEmu(const flagcxDevComm *cs, const MoeArgs *as) {
   dispatchBody(cs[blockIdx.y], as[blockIdx.y]);
 }
-__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) moeCombineKernel(const flagcxDevComm c, const MoeArgs a) {
+__global__ void __launch_bounds__(kMoeThreads) moeCombineKernel(const flagcxDevComm c, const MoeArgs a) {
   combineBody(c, a);
 }
-__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+__global__ void __launch_bounds__(kMoeThreads)
     moeCombineKernelEmu(const flagcxDevComm *cs, const MoeArgs *as) {
   combineBody(cs[blockIdx.y], as[blockIdx.y]);
 }
@@ -318,7 +374,7 @@ __global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
 } // namespace
 
 cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a) {
-  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(kMoeThreads);
   const size_t smem = 0;
   (void)a;
   if (lc.emuRanks > 0) {
@@ -331,7 +387,7 @@ cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a) {
 }
 
 cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a) {
-  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(lc.nThreads);
+  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(kMoeThreads);
   if (lc.emuRanks > 0) {
     const void *blob = lc.emuBlob;
     void *params[] = {(void *)&lc.emuComms, (void *)&blob};

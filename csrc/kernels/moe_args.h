@@ -34,7 +34,7 @@ struct MoeArgs {
   int maxT;                // largest token count any rank may pass (fixes the per-CTA share of that area)
   int dedup;               // 0: every (token, expert) pair crosses NVLink on its own (groups of one)
   int preReduce;           // combine: 1 = expert ranks pre-reduce each group, 0 = owners pull every pair
-  int *lead;               // local [T*K]: 1 where the pair leads its group
+  int *lead;               // local [T*K]: per token, the pair indices of its group leaders packed to the front, then -1
   float *wRow[FLAGCX_MAX_RANKS];     // wRow[p]: rank p's gate weight per received row (pushed by the combine)
   char *partial[FLAGCX_MAX_RANKS];   // partial[p]: rank p's pre-reduced rows, indexed by the group's leader row
   int T, H, K, E, EPR;

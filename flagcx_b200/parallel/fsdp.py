@@ -54,6 +54,11 @@ class ShardedModel:
         # one-CTA barrier kernels, which leaves every SM to the GEMMs it runs beside.
         self.gather_algo = {"push": capi.ALGO_PUSH, "copy_engine": capi.ALGO_COPY_ENGINE}[
             os.environ.get("FLAGCX_FSDP_ALLGATHER", "push")]
+        # The gradient reduce-scatter: "pull" = comm_ctas CTAs read the peers' buffers over
+        # NVLink and add; "copy_engine" = the copy engines deliver every rank's block into the
+        # owner's staging area and the same CTAs add from local memory only.
+        self.scatter_algo = {"pull": capi.ALGO_PULL, "copy_engine": capi.ALGO_COPY_ENGINE}[
+            os.environ.get("FLAGCX_FSDP_REDUCESCATTER", "pull")]
         # AdamW of a unit runs on its own stream as soon as that unit's gradients are
         # reduced, underneath the backward pass of the units before it (it is bound by
         # memory bandwidth, the backward GEMMs by the tensor cores), instead of after the
@@ -261,7 +266,7 @@ class ShardedModel:
         cs = self.comm_stream
         cs.wait_event(ev)
         self.comm.reduce_scatter_fused(self.grad_buf[b], self.grad_shard[u], self.shard_numel[u], capi.BFLOAT16, capi.AVG,
-                                       algo=capi.ALGO_PULL, nctas=self.comm_ctas, stream=cs)
+                                       algo=self.scatter_algo, nctas=self.comm_ctas, stream=cs)
         self.comm_launches += 1
         done = torch.cuda.Event()
         done.record(cs)

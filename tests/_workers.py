@@ -445,7 +445,7 @@ def gpu_nvls_collectives(rank, n, uid, count):
     return worst
 
 
-def gpu_copy_engine_allgather(rank, n, uid, count, rounds):
+def gpu_copy_engine_collectives(rank, n, uid, count, rounds):
     """All-gather into a window with the data moved by the copy engines (two one-CTA barrier
     kernels around n peer copies): exact results over several rounds that reuse the same
     output buffer with changing contents, out of place and in place, while one rank is
@@ -479,6 +479,25 @@ def gpu_copy_engine_allgather(rank, n, uid, count, rounds):
             want = torch.tensor([val(r) for r in range(n)], device="cuda")[:, None].expand(n, count)
             if not torch.equal(got, want):
                 worst[f"round{it}"] = 2.0
+        # reduce-scatter: peer copies into the owners' staging areas, then a local reduce.
+        # Plain torch tensors on both sides; a block larger than a staging slot (several
+        # chunks) and a small odd one; exact small-integer sums; average fused in.
+        for it, cnt in enumerate((count * 3 + 40, 1000, count * 3 + 40)):
+            if rank == (it + 1) % n:
+                for _ in range(20):
+                    ballast = (ballast @ ballast).clamp_(-1, 1)
+            x = torch.empty(n, cnt, dtype=torch.float32, device="cuda")
+            for blk in range(n):
+                x[blk].fill_(float(rank + 1 + blk + it))
+            y = torch.zeros(cnt, dtype=torch.float32, device="cuda")
+            comm.reduce_scatter_fused(x, y, cnt, capi.FLOAT, capi.AVG if it == 2 else capi.SUM, algo=capi.ALGO_COPY_ENGINE, nctas=8)
+            if comm.stats(capi.OP_REDUCESCATTER).lastAlgo != capi.ALGO_COPY_ENGINE:
+                worst["rs_fell_back"] = 2.0
+            want = float(sum(r + 1 + rank + it for r in range(n)))
+            if it == 2:
+                want /= n
+            if not torch.equal(y, torch.full_like(y, want)):
+                worst[f"rs_round{it}"] = 2.0
         torch.cuda.synchronize()
         if comm.async_error() != 0:
             worst["device_error"] = 2.0

@@ -61,9 +61,10 @@ def test_nvls_multimem_kernels():
 
 
 @needs2
-def test_copy_engine_allgather_with_a_straggler():
+def test_copy_engine_allgather_and_reduce_scatter_with_a_straggler():
     n = 8 if ngpus() >= 8 else 4 if ngpus() >= 4 else 2
-    res = run_ranks(n, "gpu_copy_engine_allgather", 1 << 20, 12, timeout=300)
+    # a 4 MiB staging area makes the 3 M-element reduce-scatter take several chunks
+    res = run_ranks(n, "gpu_copy_engine_collectives", 1 << 20, 12, env={"FLAGCX_STAGING_BYTES": str(4 << 20)}, timeout=300)
     for rank, worst in res.items():
         bad = {k: v for k, v in worst.items() if v > 1.0}
         assert not bad, (rank, bad)
