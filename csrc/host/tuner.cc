@@ -69,11 +69,22 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       if (ch.algo == FLAGCX_ALGO_TWOSHOT || ch.algo == FLAGCX_ALGO_NVLS_TWOSHOT) work = bytes / std::max(1, nranks);
       break;
     }
-    case flagcxCommOpReduceScatter:
+    case flagcxCommOpReduceScatter: {
       if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
       ch.algo = nvlsOk && nranks > 2 && bytes >= (1u << 20) ? FLAGCX_ALGO_NVLS : FLAGCX_ALGO_PULL;
       work = bytes / std::max(1, nranks);
+      // Callers that overlap their collectives with compute (a training framework's
+      // gradient reduce-scatter) do better with the copy engines carrying the bytes and a
+      // few CTAs adding from local memory: FLAGCX_COPY_ENGINE_MIN_BYTES > 0 asks for that
+      // from the given total size on.  The torch backend sets it (32 MiB) unless told otherwise.
+      static const int64_t ceMin = readParam("COPY_ENGINE_MIN_BYTES", 0);
+      if (ceMin > 0 && bytes >= (size_t)ceMin && nranks > 1) {
+        ch.algo = FLAGCX_ALGO_COPY_ENGINE;
+        ch.nCtas = std::min(16, maxCtas);
+        return ch;
+      }
       break;
+    }
     case flagcxCommOpAllGather:
       if (bytes / std::max(1, nranks) <= llMaxAllGather) { ch.algo = FLAGCX_ALGO_LL; break; }
       ch.algo = FLAGCX_ALGO_PUSH;
