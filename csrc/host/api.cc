@@ -1,5 +1,6 @@
-// api.cc -- the extern "C" surface: communicator life cycle, memory, collectives,
-// grouping, the one-sided host API and the extension entry points.
+// api.cc -- the extern "C" surface, part 1: communicator life cycle, memory, windows,
+// collectives and grouping (the one-sided host API is in api_onesided.cc, the extension
+// entry points of flagcx_ext.h in api_ext.cc).
 //
 // A collective call takes one of three routes:
 //   device  buffers are on the GPU and the communicator has the NVLink device
@@ -13,8 +14,7 @@
 #include <mutex>
 
 #include "../kernels/launch.h"
-#include "comm.h"
-#include "flagcx_ext.h"
+#include "api_internal.h"
 #include "tuner.h"
 
 using namespace fcx;
@@ -22,8 +22,6 @@ using namespace fcx;
 namespace {
 
 enum Route { kRouteDevice, kRouteHost, kRouteStaged };
-
-cudaStream_t rawStream(flagcxStream_t s) { return s ? s->base : nullptr; }
 
 Route routeFor(flagcxComm *c, const void *a, const void *b) {
   if (c->emu) return kRouteDevice;
@@ -60,14 +58,6 @@ flagcxResult_t hostStage(flagcxComm *c, size_t bytes, char **out) {
   *out = (char *)c->hostStage;
   return flagcxSuccess;
 }
-
-#define FCX_COMMCHECK(comm)                                                   \
-  do {                                                                        \
-    if (!commValid(comm)) {                                                   \
-      FCX_WARN("%s: invalid communicator handle", __func__);                  \
-      return flagcxInvalidArgument;                                           \
-    }                                                                         \
-  } while (0)
 
 // Runs `fn(sendHost, recvHost)` on pinned copies of device buffers.
 template <typename Fn>
@@ -342,11 +332,17 @@ flagcxResult_t flagcxWindowGetMulticastPointer(flagcxWindow_t win, size_t offset
 // ---------------------------------------------------------------------------
 // collectives
 // ---------------------------------------------------------------------------
-static flagcxResult_t checkUsable(flagcxComm *c) {
+} // extern "C"
+
+namespace fcx {
+flagcxResult_t checkUsable(flagcxComm *c) {
   if (c->finalized) { FCX_WARN("communicator was finalized or suspended"); return flagcxInvalidUsage; }
   int e = c->asyncError.load();
   return e == flagcxSuccess ? flagcxSuccess : (flagcxResult_t)e;
 }
+} // namespace fcx
+
+extern "C" {
 
 static flagcxResult_t runCollective(flagcxComm *c, DeviceCollRequest &rq, size_t sendBytes, size_t recvBytes,
                                     flagcxStream_t stream) {
@@ -586,329 +582,6 @@ flagcxResult_t flagcxGroupEnd(flagcxComm_t comm) {
   if (comm->groupDepth <= 0) { FCX_WARN("flagcxGroupEnd without flagcxGroupStart"); return flagcxInvalidUsage; }
   if (--comm->groupDepth > 0) return flagcxSuccess;
   return flushGroup(comm);
-}
-
-// ---------------------------------------------------------------------------
-// one-sided host API (ranks of one NVLink domain)
-// ---------------------------------------------------------------------------
-static int hostSignalIndex(int srcRank) { return FLAGCX_MAX_SIGNALS - FLAGCX_MAX_RANKS + srcRank; }
-
-flagcxResult_t flagcxOneSideRegister(flagcxComm_t comm, void *buff, size_t size) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  Window *w = comm->windows.find(buff, size);
-  const bool created = w == nullptr;
-  if (!w) {
-    if (comm->emu) FCXCHECK(emuWindowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
-    else FCXCHECK(windowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
-  }
-  comm->oneSideData.push_back(w);
-  comm->oneSideOwned.push_back(created ? 1 : 0);
-  return flagcxSuccess;
-}
-
-// Collective: forgets every memory region of flagcxOneSideRegister (indices start at 0
-// again) and unmaps the windows that call created.  Declared in
-// flagcx_kernel_internal.h in the FlagCX project.
-flagcxResult_t flagcxOneSideDeregister(flagcxComm_t comm) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  flagcxResult_t first = flagcxSuccess;
-  for (size_t i = 0; i < comm->oneSideData.size(); ++i) {
-    if (!comm->oneSideOwned[i]) continue;
-    flagcxResult_t r = flagcxCommWindowDeregister(comm, (flagcxWindow_t)comm->oneSideData[i], flagcxMemCCL);
-    if (r != flagcxSuccess && first == flagcxSuccess) first = r;
-  }
-  comm->oneSideData.clear();
-  comm->oneSideOwned.clear();
-  return first;
-}
-flagcxResult_t flagcxOneSideSignalDeregister(flagcxComm_t comm) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  flagcxResult_t r = flagcxSuccess;
-  if (comm->oneSideSignalWin) r = flagcxCommWindowDeregister(comm, (flagcxWindow_t)comm->oneSideSignalWin, flagcxMemCCL);
-  comm->oneSideSignalWin = nullptr;
-  return r;
-}
-flagcxResult_t flagcxOneSideSignalRegister(const flagcxComm_t comm, void *buff, size_t size, int) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  Window *w = nullptr;
-  if (comm->emu) FCXCHECK(emuWindowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
-  else FCXCHECK(windowRegister(comm, buff, size, FLAGCX_WIN_COLL_SYMMETRIC, &w));
-  comm->oneSideSignalWin = w;
-  return flagcxSuccess;
-}
-// NVLink puts need no bounce buffer; the calls are accepted so callers keep working.
-flagcxResult_t flagcxOneSideStagingRegister(const flagcxComm_t comm, void *, size_t) {
-  FCX_COMMCHECK(comm);
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxOneSideStagingDeregister(const flagcxComm_t comm) {
-  FCX_COMMCHECK(comm);
-  return flagcxSuccess;
-}
-
-static flagcxResult_t rmaCopy(flagcxComm *c, bool isPut, int peer, size_t srcOff, size_t dstOff, size_t size,
-                              int srcMr, int dstMr) {
-  if (!c->devicePath) return flagcxNotSupported;
-  FCX_ARGCHECK(peer >= 0 && peer < c->nranks && srcMr >= 0 && dstMr >= 0 && srcMr < (int)c->oneSideData.size() &&
-                   dstMr < (int)c->oneSideData.size(),
-               "put/get: bad peer or memory-region index");
-  Window *sw = c->oneSideData[srcMr], *dw = c->oneSideData[dstMr];
-  FCX_ARGCHECK(srcOff + size <= sw->size && dstOff + size <= dw->size, "put/get: range outside the registered region");
-  // put: local src -> peer's dst.  get: peer's src -> local dst.
-  const char *src = (const char *)(isPut ? sw->peer[c->rank] : sw->peer[peer]) + srcOff;
-  char *dst = (char *)(isPut ? dw->peer[peer] : dw->peer[c->rank]) + dstOff;
-  cudaError_t e = launchPutSignal(c->internalStream, dst, src, size, nullptr, 0, c->putArrival, 8);
-  if (e != cudaSuccess) { FCX_WARN("put/get launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
-  c->rmaIssued++;
-  // completion counter the host can read without touching the stream
-  void *dptr = nullptr;
-  FCX_CUDACHECK(cudaHostGetDevicePointer(&dptr, (void *)c->rmaCounter, 0));
-  return cu::streamWriteValue64(c->internalStream, dptr, c->rmaIssued);
-}
-
-flagcxResult_t flagcxPut(flagcxComm_t comm, int peer, size_t srcOffset, size_t dstOffset, size_t size, int srcMrIdx,
-                         int dstMrIdx) {
-  FCX_COMMCHECK(comm);
-  return rmaCopy(comm, true, peer, srcOffset, dstOffset, size, srcMrIdx, dstMrIdx);
-}
-flagcxResult_t flagcxGet(flagcxComm_t comm, int peer, size_t srcOffset, size_t dstOffset, size_t size, int srcMrIdx,
-                         int dstMrIdx) {
-  FCX_COMMCHECK(comm);
-  return rmaCopy(comm, false, peer, srcOffset, dstOffset, size, srcMrIdx, dstMrIdx);
-}
-flagcxResult_t flagcxBatchPut(flagcxComm_t comm, int peer, const size_t *srcOffsets, const size_t *dstOffsets,
-                              const size_t *sizes, const int *srcMrIdxs, const int *dstMrIdxs, size_t count) {
-  FCX_COMMCHECK(comm);
-  for (size_t i = 0; i < count; ++i)
-    FCXCHECK(rmaCopy(comm, true, peer, srcOffsets[i], dstOffsets[i], sizes[i], srcMrIdxs[i], dstMrIdxs[i]));
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxReadCounter(flagcxComm_t comm, uint64_t *count) {
-  FCX_COMMCHECK(comm);
-  if (!comm->rmaCounter || !count) return flagcxNotSupported;
-  *count = *comm->rmaCounter;
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxWaitCounter(flagcxComm_t comm, uint64_t target) {
-  FCX_COMMCHECK(comm);
-  if (!comm->rmaCounter) return flagcxNotSupported;
-  uint64_t deadline = nowNs() + comm->dev.timeoutNs;
-  while (*comm->rmaCounter < target) {
-    if (nowNs() > deadline) { FCX_WARN("flagcxWaitCounter: %llu not reached in time", (unsigned long long)target); return flagcxRemoteError; }
-    sched_yield();
-  }
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxPutSignal(const void *localbuff, size_t count, flagcxDataType_t datatype, int peer,
-                               flagcxWindow_t peerWin, size_t peerWinOffset, unsigned int, flagcxComm_t comm,
-                               flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  Window *w = (Window *)peerWin;
-  size_t bytes = count * getFlagcxDataTypeSize(datatype);
-  FCX_ARGCHECK(w && peer >= 0 && peer < comm->nranks && peerWinOffset + bytes <= w->size, "putSignal: bad argument");
-  unsigned long long *sig = comm->dev.signalPad[peer] + hostSignalIndex(comm->rank);
-  int ctas = (int)std::max<size_t>(1, std::min<size_t>(bytes >> 16, 32));
-  cudaError_t e = launchPutSignal(rawStream(stream), (char *)w->peer[peer] + peerWinOffset, localbuff, bytes, sig, 1,
-                                  comm->putArrival, ctas);
-  if (e != cudaSuccess) { FCX_WARN("putSignal launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
-  comm->signalSent[peer]++;
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxSignal(int peer, unsigned int, flagcxComm_t comm, flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  FCX_ARGCHECK(peer >= 0 && peer < comm->nranks, "signal: bad peer");
-  unsigned long long *sig = comm->dev.signalPad[peer] + hostSignalIndex(comm->rank);
-  cudaError_t e = launchPutSignal(rawStream(stream), nullptr, nullptr, 0, sig, 1, comm->putArrival, 1);
-  if (e != cudaSuccess) return flagcxUnhandledDeviceError;
-  comm->signalSent[peer]++;
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxWaitSignal(int nDesc, const flagcxWaitSignalDesc_t *descs, flagcxComm_t comm,
-                                flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  if (!comm->devicePath) return flagcxNotSupported;
-  for (int i = 0; i < nDesc; ++i) {
-    int peer = descs[i].peer;
-    FCX_ARGCHECK(peer >= 0 && peer < comm->nranks, "waitSignal: bad peer");
-    comm->signalSeen[peer] += descs[i].opCnt;
-    const unsigned long long *sig = comm->dev.signalPad[comm->rank] + hostSignalIndex(peer);
-    cudaError_t e = launchWaitSignal(rawStream(stream), comm->dev, sig, comm->signalSeen[peer], (unsigned)peer);
-    if (e != cudaSuccess) return flagcxUnhandledDeviceError;
-  }
-  return flagcxSuccess;
-}
-
-// ---------------------------------------------------------------------------
-// extensions
-// ---------------------------------------------------------------------------
-// Device collective of the extension entry points, with the same trace record and NVTX range
-// that the FlagCX-compatible entry points get.
-static flagcxResult_t tracedDeviceCollective(flagcxComm *c, const DeviceCollRequest &rq, size_t bytes, flagcxStream_t stream) {
-  nvtxPush(commOpName(rq.op));
-  const int slot = c->trace.begin(c, rq.op, bytes, 0, rawStream(stream));
-  flagcxResult_t r = deviceCollective(c, rq, rawStream(stream));
-  c->trace.end(c, slot, rawStream(stream));
-  nvtxPop();
-  return r;
-}
-
-flagcxResult_t flagcxAllReduceFused(const void *sendbuff, void *recvbuff, size_t count, flagcxDataType_t datatype,
-                                    flagcxRedOp_t op, const flagcxFusedOpts_t *opts, flagcxComm_t comm,
-                                    flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  FCXCHECK(checkUsable(comm));
-  if (!comm->devicePath) return flagcxNotSupported;
-  DeviceCollRequest rq{flagcxCommOpAllReduce, sendbuff, recvbuff, count, datatype, op, 0};
-  if (opts) {
-    rq.scale = opts->scale;
-    rq.outDtype = opts->outDtype;
-    rq.residual = opts->residual;
-    rq.algo = opts->algo;
-    rq.nCtas = opts->nCtas > 0 ? opts->nCtas : -1;
-  }
-  return tracedDeviceCollective(comm, rq, count * getFlagcxDataTypeSize(datatype), stream);
-}
-
-flagcxResult_t flagcxReduceScatterFused(const void *sendbuff, void *recvbuff, size_t recvcount,
-                                        flagcxDataType_t datatype, flagcxRedOp_t op, const flagcxFusedOpts_t *opts,
-                                        flagcxComm_t comm, flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  FCXCHECK(checkUsable(comm));
-  if (!comm->devicePath) return flagcxNotSupported;
-  DeviceCollRequest rq{flagcxCommOpReduceScatter, sendbuff, recvbuff, recvcount, datatype, op, 0};
-  if (opts) {
-    rq.scale = opts->scale;
-    rq.outDtype = opts->outDtype;
-    rq.residual = opts->residual;
-    rq.algo = opts->algo;
-    rq.nCtas = opts->nCtas > 0 ? opts->nCtas : -1;
-  }
-  return tracedDeviceCollective(comm, rq, recvcount * getFlagcxDataTypeSize(datatype) * comm->nranks, stream);
-}
-
-flagcxResult_t flagcxAllGatherEx(const void *sendbuff, void *recvbuff, size_t sendcount, flagcxDataType_t datatype,
-                                 int algo, int nCtas, flagcxComm_t comm, flagcxStream_t stream) {
-  FCX_COMMCHECK(comm);
-  FCXCHECK(checkUsable(comm));
-  if (!comm->devicePath) return flagcxNotSupported;
-  DeviceCollRequest rq{flagcxCommOpAllGather, sendbuff, recvbuff, sendcount, datatype, flagcxSum, 0};
-  rq.algo = algo;
-  rq.nCtas = nCtas > 0 ? nCtas : -1;
-  return tracedDeviceCollective(comm, rq, sendcount * getFlagcxDataTypeSize(datatype) * comm->nranks, stream);
-}
-
-flagcxResult_t flagcxTunerTune(flagcxComm_t comm, flagcxCommOp_t op, flagcxDataType_t dtype, size_t minBytes,
-                               size_t maxBytes, int iters) {
-  FCX_COMMCHECK(comm);
-  if (!comm->tuner) return flagcxNotSupported;
-  return comm->tuner->tune(comm, op, dtype, minBytes, maxBytes, iters);
-}
-flagcxResult_t flagcxTunerSave(flagcxComm_t comm, const char *path) {
-  FCX_COMMCHECK(comm);
-  if (!comm->tuner || !path) return flagcxNotSupported;
-  return comm->tuner->save(path);
-}
-flagcxResult_t flagcxTunerLoad(flagcxComm_t comm, const char *path) {
-  FCX_COMMCHECK(comm);
-  if (!comm->tuner || !path) return flagcxNotSupported;
-  return comm->tuner->load(path);
-}
-flagcxResult_t flagcxTunerQuery(flagcxComm_t comm, flagcxCommOp_t op, size_t bytes, int registered, int *algo,
-                                int *nCtas) {
-  FCX_COMMCHECK(comm);
-  if (!comm->tuner) return flagcxNotSupported;
-  TuneChoice ch = comm->tuner->choose(op, bytes, comm->nranks, registered != 0, comm->nvls);
-  if (algo) *algo = ch.algo;
-  if (nCtas) *nCtas = ch.nCtas;
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxCommTraceEnable(flagcxComm_t comm, int capacity) {
-  FCX_COMMCHECK(comm);
-  if (capacity < 0 || capacity > (1 << 20)) return flagcxInvalidArgument;
-  comm->trace.enable(capacity);
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxCommTraceDump(flagcxComm_t comm, const char *path) {
-  FCX_COMMCHECK(comm);
-  if (!comm->trace.on()) return flagcxInvalidUsage;
-  return comm->trace.dump(comm, path);
-}
-
-flagcxResult_t flagcxCommGetStats(flagcxComm_t comm, flagcxCommOp_t op, flagcxOpStats_t *out) {
-  FCX_COMMCHECK(comm);
-  if (!out || (int)op < 0 || op >= flagcxNumCommOps) return flagcxInvalidArgument;
-  const OpStats &s = comm->stats[op];
-  out->calls = s.calls;
-  out->bytes = s.bytes;
-  out->lastAlgo = s.lastAlgo;
-  out->lastCtas = s.lastCtas;
-  out->lastMs = s.lastMs;
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommUserBufferStats(flagcxComm_t comm, flagcxUserBufferStats_t *out) {
-  FCX_COMMCHECK(comm);
-  if (!out) return flagcxInvalidArgument;
-  memset(out, 0, sizeof *out);
-  out->enabled = comm->exportUserBuffers ? 1 : 0;
-  if (comm->reg) {
-    RegCache::Counters k = comm->reg->counters();
-    out->hits = k.hits;
-    out->exports = k.exports;
-    out->refused = k.refused;
-    out->stale = k.stale;
-    out->peerOpened = k.opened;
-    out->peerClosed = k.closed;
-  }
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommSetAutoExport(flagcxComm_t comm, int on) {
-  FCX_COMMCHECK(comm);
-  comm->autoExport = on != 0 && comm->exportUserBuffers;
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommForgetUserBuffer(flagcxComm_t comm, const void *ptr) {
-  FCX_COMMCHECK(comm);
-  if (comm->reg && ptr) comm->reg->forget(ptr);
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommIsDevicePath(flagcxComm_t comm, int *yes) {
-  FCX_COMMCHECK(comm);
-  *yes = comm->devicePath ? 1 : 0;
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommHasMulticast(flagcxComm_t comm, int *yes) {
-  FCX_COMMCHECK(comm);
-  *yes = (comm->internalWin && comm->internalWin->mc) ? 1 : 0;
-  return flagcxSuccess;
-}
-flagcxResult_t flagcxCommSetWaitTimeoutMs(flagcxComm_t comm, int ms) {
-  FCX_COMMCHECK(comm);
-  comm->dev.timeoutNs = (unsigned long long)std::max(ms, 1) * 1000000ull;
-  return flagcxSuccess;
-}
-
-flagcxResult_t flagcxEmuWorldCreate(int nranks, int device, flagcxComm_t *comms) {
-  if (!comms) return flagcxInvalidArgument;
-  return emuWorldCreate(nranks, device, comms);
-}
-flagcxResult_t flagcxEmuWorldDestroy(flagcxComm_t anyRank) {
-  FCX_COMMCHECK(anyRank);
-  return emuWorldDestroy(anyRank);
-}
-
-flagcxResult_t flagcxHostReduce(void *dst, const void *src, size_t count, flagcxDataType_t dtype, flagcxRedOp_t op) {
-  return hostReduce(dst, src, count, dtype, op);
 }
 
 } // extern "C"

@@ -18,6 +18,7 @@
 #include "../host/shm.h"
 #include "../host/tuner.h"
 #include "flagcx_net.h"
+#include "flagcx_p2p.h"
 
 using namespace fcx;
 
@@ -366,6 +367,65 @@ static void testRegCache() {
   allocs.clear();
 }
 
+// Two transfer engines in one process (host memory): an owner thread that accepts and
+// waits for notifications, an initiator that writes, looks ranges up by address, reads
+// back, and provokes the two range errors.  Under the sanitizers this is the check of the
+// engine's threads (accept loop, per-connection service thread, requester).
+static void testP2pEngine() {
+  flagcxP2pEngine_t owner = nullptr, user = nullptr;
+  EXPECT(flagcxP2pEngineCreate(-1, &owner) == flagcxSuccess);
+  EXPECT(flagcxP2pEngineCreate(-1, &user) == flagcxSuccess);
+  if (!owner || !user) return;
+  std::vector<unsigned char> mem(1 << 18, 0), src(1 << 18), back(1 << 18, 0);
+  for (size_t i = 0; i < src.size(); ++i) src[i] = (unsigned char)(i * 7 + 3);
+  flagcxP2pMr_t mr = 0;
+  EXPECT(flagcxP2pEngineReg(owner, mem.data(), mem.size(), &mr) == flagcxSuccess);
+  flagcxP2pDesc_t whole;
+  EXPECT(flagcxP2pEngineMakeDesc(owner, mr, mem.data(), mem.size(), &whole) == flagcxSuccess);
+  EXPECT(flagcxP2pEngineMakeDesc(owner, mr, mem.data() + mem.size() - 8, 16, &whole) == flagcxInvalidArgument);
+  EXPECT(flagcxP2pEngineMakeDesc(owner, mr, mem.data(), mem.size(), &whole) == flagcxSuccess);
+  char meta[128];
+  EXPECT(flagcxP2pEngineGetMetadata(owner, meta, sizeof meta) == flagcxSuccess);
+  std::atomic<int> ownerOk{0};
+  std::thread ownerThread([&] {
+    flagcxP2pConn_t c = nullptr;
+    if (flagcxP2pEngineAccept(owner, &c, 20000) != flagcxSuccess) return;
+    char msg[64];
+    size_t len = 0;
+    if (flagcxP2pRecvNotif(c, msg, sizeof msg, &len, 20000) == flagcxSuccess && len == 4 && !memcmp(msg, "done", 4) &&
+        !memcmp(mem.data(), src.data(), mem.size()))
+      ownerOk.store(1);
+    flagcxP2pSendNotif(c, "ok", 2);
+    // the peer says goodbye by closing; wait for that so that its reads are served
+    flagcxResult_t r = flagcxP2pRecvNotif(c, msg, sizeof msg, &len, 20000);
+    if (r == flagcxRemoteError) ownerOk.fetch_add(1);
+    flagcxP2pConnDestroy(c);
+  });
+  flagcxP2pConn_t c = nullptr;
+  EXPECT(flagcxP2pEngineConnect(user, meta, &c) == flagcxSuccess);
+  if (c) {
+    int local = 0;
+    EXPECT(flagcxP2pConnIsLocal(c, &local) == flagcxSuccess && local == 1);
+    EXPECT(flagcxP2pWrite(c, src.data(), &whole, src.size(), nullptr) == flagcxSuccess);
+    EXPECT(flagcxP2pSendNotif(c, "done", 4) == flagcxSuccess);
+    char msg[8];
+    size_t len = 0;
+    EXPECT(flagcxP2pRecvNotif(c, msg, sizeof msg, &len, 20000) == flagcxSuccess && len == 2);
+    flagcxP2pDesc_t part;
+    EXPECT(flagcxP2pConnLookup(c, (uint64_t)(uintptr_t)mem.data() + 1000, 5000, &part) == flagcxSuccess);
+    EXPECT(flagcxP2pRead(c, back.data(), &part, 5000, nullptr) == flagcxSuccess && !memcmp(back.data(), src.data() + 1000, 5000));
+    EXPECT(flagcxP2pRead(c, back.data(), &part, 5001, nullptr) == flagcxInvalidArgument);
+    EXPECT(flagcxP2pConnLookup(c, (uint64_t)(uintptr_t)mem.data() + mem.size() - 4, 64, &part) == flagcxInvalidArgument);
+    EXPECT(flagcxP2pRecvNotif(c, msg, sizeof msg, &len, 10) == flagcxInProgress);
+    EXPECT(flagcxP2pConnDestroy(c) == flagcxSuccess);
+  }
+  ownerThread.join();
+  EXPECT(ownerOk.load() == 2);
+  EXPECT(flagcxP2pEngineDereg(owner, mr) == flagcxSuccess);
+  EXPECT(flagcxP2pEngineDestroy(user) == flagcxSuccess);
+  EXPECT(flagcxP2pEngineDestroy(owner) == flagcxSuccess);
+}
+
 int main() {
   testRegCache();
   testShmRing();
@@ -379,6 +439,7 @@ int main() {
   testSocketAdaptor();
   testBootstrapThreads();
   testCommunicatorsInThreads();
+  testP2pEngine();
   printf("%s: %d failure(s)\n", failures ? "FAILED" : "ok", failures);
   return failures;
 }

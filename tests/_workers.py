@@ -969,3 +969,103 @@ def sp_ulysses_and_ring(rank, n, uid, S, H, D, use_cuda=False):
     comm.barrier()
     comm.destroy()
     return out
+
+
+def p2p_engine_pair(rank, n, uid_unused, path, use_cuda):
+    """Two processes that share no communicator: rank 0 owns a registered buffer, rank 1
+    writes and reads it one-sidedly (whole, by looked-up address, as a vector), both trade
+    notifications; bad ranges come back as error codes."""
+    import json
+    import os
+    import time
+    from flagcx_b200.p2p import P2pEngine
+    N = 1 << 20
+    if use_cuda:
+        import torch
+        ndev = torch.cuda.device_count()
+        dev = rank % ndev
+        torch.cuda.set_device(dev)
+        zeros = lambda k: torch.zeros(k, dtype=torch.uint8, device="cuda")
+        pattern = lambda k, seed: ((torch.arange(k, device="cuda", dtype=torch.int64) * (seed * 2 + 1) + seed) % 251).to(torch.uint8)
+        equal = lambda a, b: bool(torch.equal(a, b))
+        addr = lambda t: t.data_ptr()
+        eng = P2pEngine(dev)
+    else:
+        zeros = lambda k: np.zeros(k, np.uint8)
+        pattern = lambda k, seed: ((np.arange(k, dtype=np.int64) * (seed * 2 + 1) + seed) % 251).astype(np.uint8)
+        equal = lambda a, b: bool(np.array_equal(a, b))
+        addr = lambda t: t.ctypes.data
+        eng = P2pEngine(-1)
+    out = {}
+    if rank == 0:
+        buf = zeros(N)
+        mr = eng.register(buf)
+        with open(path + ".tmp", "w") as f:
+            json.dump({"meta": eng.metadata, "desc": eng.describe(mr, buf).hex(), "addr": addr(buf)}, f)
+        os.replace(path + ".tmp", path)
+        conn = eng.accept(60000)
+        assert conn is not None, "nobody connected"
+        assert conn.recv_notification(60000) == b"whole buffer written"
+        if use_cuda:
+            torch.cuda.synchronize()
+        out["whole_write"] = float(not equal(buf, pattern(N, 1)))
+        conn.notify(b"checked")  # the writer goes on only now: the next writes change the buffer
+        assert conn.recv_notification(60000) == b"pieces written"
+        want = pattern(N, 1)
+        want[4096:4096 + 100] = pattern(100, 2)
+        for i in range(3):
+            want[65536 * (i + 1): 65536 * (i + 1) + 1000 + i] = pattern(1000 + i, 3 + i)
+        if use_cuda:
+            torch.cuda.synchronize()
+        out["piece_writes"] = float(not equal(buf, want))
+        buf[:] = pattern(N, 9)
+        if use_cuda:
+            torch.cuda.synchronize()
+        conn.notify(b"read me")
+        assert conn.recv_notification(60000) == b"bye"
+        out["is_local"] = float(not conn.is_local)
+        conn.close()
+        eng.deregister(mr)
+    else:
+        deadline = time.time() + 60
+        while not os.path.exists(path):
+            assert time.time() < deadline, "the owner never published its metadata"
+            time.sleep(0.05)
+        info = json.load(open(path))
+        desc = bytes.fromhex(info["desc"])
+        conn = eng.connect(info["meta"])
+        conn.write(pattern(N, 1), desc)
+        conn.notify(b"whole buffer written")
+        assert conn.recv_notification(60000) == b"checked"
+        small = conn.lookup(info["addr"] + 4096, 100)  # by the owner's virtual address
+        conn.write(pattern(100, 2), small)
+        pieces = [pattern(1000 + i, 3 + i) for i in range(3)]
+        conn.write_vector(pieces, [conn.lookup(info["addr"] + 65536 * (i + 1), 1000 + i) for i in range(3)])
+        conn.notify(b"pieces written")
+        assert conn.recv_notification(60000) == b"read me"
+        got = zeros(N)
+        conn.read(got, desc)
+        if use_cuda:
+            torch.cuda.synchronize()
+        out["whole_read"] = float(not equal(got, pattern(N, 9)))
+        parts = [zeros(512), zeros(700)]
+        conn.read_vector(parts, [conn.lookup(info["addr"] + 10, 512), conn.lookup(info["addr"] + N - 700, 700)])
+        out["vector_read"] = float(not (equal(parts[0], pattern(N, 9)[10:522]) and equal(parts[1], pattern(N, 9)[N - 700:])))
+        # errors, not faults: a range outside every registered region, more bytes than the descriptor covers
+        for name, fn in (("lookup_outside", lambda: conn.lookup(info["addr"] + N - 10, 100)),
+                         ("write_too_long", lambda: conn.write(zeros(200), small, nbytes=200))):
+            try:
+                fn()
+                out[name] = 2.0
+            except capi.FlagcxError:
+                out[name] = 0.0
+        # the connection still works afterwards
+        conn.read(parts[0], conn.lookup(info["addr"], 512))
+        out["after_errors"] = float(not equal(parts[0], pattern(N, 9)[:512]))
+        assert conn.recv_notification(10) is None  # nothing pending: times out cleanly
+        out["is_local"] = float(not conn.is_local)
+        conn.notify(b"bye")
+        conn.close()
+    eng.close()
+    return out
+
