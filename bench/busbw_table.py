@@ -36,7 +36,11 @@ def load(path: str):
         for line in f:
             line = line.strip()
             if line.startswith("{"):
-                rows.append(json.loads(line))
+                r = json.loads(line)
+                # single-implementation files (--impl reference / nccl / ours_pg) name their columns "us" / "busbw"
+                r.setdefault("ours_us", r.get("us"))
+                r.setdefault("ours_busbw", r.get("busbw"))
+                rows.append(r)
     return rows
 
 

@@ -74,7 +74,7 @@ def main():
         print(f"{'op':>14} {'path':>7} {'ctas':>5} {'us':>9} {'busGB/s':>9}", flush=True)
     ops = args.ops.split(",")
     if "allreduce" in ops:
-        algos = [("twoshot", capi.ALGO_TWOSHOT)] + ([("nvls", capi.ALGO_NVLS_TWOSHOT)] if w.comm.has_multicast() else [])
+        algos = [("twoshot", capi.ALGO_TWOSHOT)] + ([("nvls", capi.ALGO_NVLS_TWOSHOT)] if w.comm.has_multicast else [])
         for path, algo in algos:
             for ctas in [int(x) for x in args.ctas.split(",")]:
                 fn = lambda: w.comm.all_reduce_fused(src, dst, total, capi.BFLOAT16, capi.SUM, algo=algo, nctas=ctas)

@@ -71,7 +71,19 @@ void fillArgs(flagcxMoe *m, MoeArgs &a, int nTokens) {
   a.grpRecordsPerSender = m->grpRecordsPerSender;
   a.maxT = m->maxTokens;
   a.dedup = readParam("MOE_DEDUP", 1) != 0 ? 1 : 0;
-  a.preReduce = readParam("MOE_COMBINE_REDUCE", 1) != 0 ? 1 : 0;
+  // Pre-reducing on the expert rank pays when a token has, on average, at least two experts
+  // per rank it goes to (one row crosses NVLink instead of two or more; 523 -> 370 us on two
+  // B200s with 64 experts, top-8); with eight ranks, 256 experts and top-8 a token reaches
+  // 5.25 ranks, the saving is a third, and the extra local pass and barrier cost more (885
+  // against 692 us).  Expected ranks per token for uniform routing: n (1 - (1 - 1/n)^k).
+  {
+    const double n = c->nranks, k = m->topk;
+    double miss = 1.0;
+    for (int i = 0; i < m->topk; ++i) miss *= 1.0 - 1.0 / n;
+    const double ranksPerToken = n * (1.0 - miss);
+    const int64_t dflt = k / ranksPerToken >= 2.0 ? 1 : 0;
+    a.preReduce = readParam("MOE_COMBINE_REDUCE", dflt) != 0 ? 1 : 0;
+  }
   a.lead = m->lead;
   a.pos = m->pos;
   a.route = m->route;
@@ -95,7 +107,13 @@ cudaError_t emuCombine(const LaunchCtx &lc, const void *d) {
   LaunchCtx l2 = lc;
   l2.emuBlob = d;
   MoeArgs dummy{};
-  return launchMoeCombine(l2, dummy);
+  return launchMoeCombine(l2, dummy, false);
+}
+cudaError_t emuCombinePull(const LaunchCtx &lc, const void *d) {
+  LaunchCtx l2 = lc;
+  l2.emuBlob = d;
+  MoeArgs dummy{};
+  return launchMoeCombine(l2, dummy, true);
 }
 
 int moeCtas(flagcxComm *c) {
@@ -212,12 +230,13 @@ flagcxResult_t flagcxMoeCombine(flagcxMoe_t m, const float *topkWeights, void *o
   a.topkIdx = m->lastIdx;
   a.topkW = topkWeights;
   a.out = (__nv_bfloat16 *)out;
-  if (c->emu) return emuSubmitBlob(c, 101, &a, sizeof a, moeCtas(c), s, emuCombine);
+  const bool pull = a.preReduce == 0;
+  if (c->emu) return emuSubmitBlob(c, pull ? 102 : 101, &a, sizeof a, moeCtas(c), s, pull ? emuCombinePull : emuCombine);
   LaunchCtx lc;
   lc.comm = &c->dev;
   lc.stream = s;
   lc.nCtas = moeCtas(c);
-  cudaError_t e = launchMoeCombine(lc, a);
+  cudaError_t e = launchMoeCombine(lc, a, pull);
   if (e != cudaSuccess) { FCX_WARN("moe combine launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;
 }

@@ -103,7 +103,11 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
   (void)registered;
   // work per CTA below which another CTA costs more (its barrier flags on every peer)
   // than it brings; the offline tuner on B200 pairs picked 8 CTAs for 1-2 MiB
-  static const size_t perCta = (size_t)std::max<int64_t>(1024, readParam("BYTES_PER_CTA", 64 << 10));
+  // (FLAGCX_BYTES_PER_CTA is that figure for a pair).  With more ranks a CTA's work splits
+  // into n-1 streams and the tuner wants more CTAs for the same bytes: 16-64 CTAs for a
+  // 1-8 MiB all-reduce or reduce-scatter on eight B200s, i.e. about 16 KiB each.
+  static const size_t perCtaPair = (size_t)std::max<int64_t>(1024, readParam("BYTES_PER_CTA", 64 << 10));
+  const size_t perCta = std::max<size_t>(8 << 10, perCtaPair * 2 / (size_t)std::max(2, nranks));
   // all-to-all moves n separate streams per CTA and keeps gaining up to about 96 CTAs
   // (365 GB/s at 32, 616 at 96 on a B200 pair, 1 GiB); everything else is flat beyond 32
   size_t cap = op == flagcxCommOpAlltoAll && work >= (16u << 20)

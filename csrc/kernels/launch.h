@@ -23,7 +23,7 @@ struct LaunchCtx {
 
 struct MoeArgs;
 cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a);
-cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a);
+cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a, bool pull);
 
 cudaError_t launchReduceKernel(const LaunchCtx &lc, const CollArgs &a, int nRanks);
 cudaError_t launchCopyKernel(const LaunchCtx &lc, const CollArgs &a);

