@@ -368,7 +368,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   // Small messages: no barrier, no registration, any buffer.  The choice depends only on
   // what every rank knows (size, type, settings, tuner table), so all ranks agree on it.
   {
-    TuneChoice pre = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, true, false);
+    TuneChoice pre = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, true, false, (int)es);
     const int want = rq.algo >= 0 ? rq.algo : pre.algo;
     if (want == FLAGCX_ALGO_LL && n > 1 && count > 0 && a.outMode == kOutSame && !a.residual &&
         count * es <= c->layout.llSlotBytes / 2) {
@@ -387,7 +387,7 @@ flagcxResult_t allReduce(flagcxComm *c, const DeviceCollRequest &rq, cudaStream_
   else FCXCHECK(resolve(c, rq.recv, count * oes, 1, stream, &uout));
   const bool inVis = uin.visible(), outVis = uout.visible();
   const bool nvlsOk = nvlsEligible(c, rq, count);
-  TuneChoice ch = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, inVis && outVis, nvlsOk);
+  TuneChoice ch = c->tuner->choose(flagcxCommOpAllReduce, count * es, n, inVis && outVis, nvlsOk, (int)es);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if ((algo == FLAGCX_ALGO_NVLS_ONESHOT || algo == FLAGCX_ALGO_NVLS_TWOSHOT) && !nvlsOk) algo = FLAGCX_ALGO_TWOSHOT;
   if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_ONESHOT; // not eligible above
@@ -528,7 +528,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   FCXCHECK(setReduceEpilogue(c, a, rq));
   const size_t es = a.elemSize, oes = outElemSize(a), count = rq.count;
   if (n > 1 && count > 0 && a.outMode == kOutSame && !a.residual && count * es <= c->layout.llSlotBytes / 2) {
-    TuneChoice pre = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, true, false);
+    TuneChoice pre = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, true, false, (int)es);
     if ((rq.algo >= 0 ? rq.algo : pre.algo) == FLAGCX_ALGO_LL) {
       a.kind = kLlReduceScatter;
       a.count = count;
@@ -544,7 +544,7 @@ flagcxResult_t reduceScatter(flagcxComm *c, const DeviceCollRequest &rq, cudaStr
   FCXCHECK(resolve(c, rq.send, count * es * n, 0, stream, &uin));
   const bool inVis = uin.visible();
   const bool nvlsOk = nvlsEligible(c, rq, count) && uin.view.win && uin.view.win->mc;
-  TuneChoice ch = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, inVis, nvlsOk);
+  TuneChoice ch = c->tuner->choose(flagcxCommOpReduceScatter, count * es * n, n, inVis, nvlsOk, (int)es);
   int algo = rq.algo >= 0 ? rq.algo : ch.algo;
   if (algo == FLAGCX_ALGO_NVLS && !nvlsOk) algo = FLAGCX_ALGO_PULL;
   if (algo == FLAGCX_ALGO_LL) algo = FLAGCX_ALGO_PULL; // not eligible above
@@ -640,7 +640,7 @@ flagcxResult_t reduceToRoot(flagcxComm *c, const DeviceCollRequest &rq, cudaStre
   UserBuf uin;
   FCXCHECK(resolve(c, rq.send, count * es, 0, stream, &uin));
   const bool inVis = uin.visible();
-  TuneChoice ch = c->tuner->choose(flagcxCommOpReduce, count * es, n, inVis, false);
+  TuneChoice ch = c->tuner->choose(flagcxCommOpReduce, count * es, n, inVis, false, (int)es);
   const int nCtas = pickCtas(c, rq, ch);
   note(c, flagcxCommOpReduce, count * es, FLAGCX_ALGO_PULL, nCtas);
   if (inVis) {

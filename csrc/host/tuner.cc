@@ -23,8 +23,13 @@ int Tuner::bucketOf(size_t bytes) {
   return b;
 }
 
-static int keyOf(flagcxCommOp_t op, int bucket, bool registered) {
-  return (int)op * 1000 + bucket * 2 + (registered ? 1 : 0);
+static int keyOf(flagcxCommOp_t op, int bucket, bool registered, int elemSize = 0) {
+  return elemSize * 100000 + (int)op * 1000 + bucket * 2 + (registered ? 1 : 0);
+}
+// Only reductions do arithmetic per element; everything else is keyed size-agnostic.
+static int elemClass(flagcxCommOp_t op, int elemSize) {
+  const bool reduces = op == flagcxCommOpAllReduce || op == flagcxCommOpReduceScatter || op == flagcxCommOpReduce;
+  return reduces && elemSize > 0 && elemSize <= 8 ? elemSize : 0;
 }
 
 flagcxResult_t Tuner::init(flagcxComm *c) {
@@ -117,9 +122,12 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
   return ch;
 }
 
-TuneChoice Tuner::choose(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk) const {
+TuneChoice Tuner::choose(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk, int elemSize) const {
   TuneChoice ch = heuristic(op, bytes, nranks, registered, nvlsOk);
-  auto it = table.find(keyOf(op, bucketOf(bytes), registered));
+  const int bucket = bucketOf(bytes);
+  auto it = table.find(keyOf(op, bucket, registered, elemClass(op, elemSize)));
+  if (it == table.end()) it = table.find(keyOf(op, bucket, registered, 0));
+  for (int es = 1; it == table.end() && es <= 8; es *= 2) it = table.find(keyOf(op, bucket, registered, es));
   if (it != table.end()) {
     bool needsNvls = it->second.algo == FLAGCX_ALGO_NVLS_ONESHOT || it->second.algo == FLAGCX_ALGO_NVLS_TWOSHOT ||
                      it->second.algo == FLAGCX_ALGO_NVLS;
@@ -138,10 +146,10 @@ std::string Tuner::toJson() const {
   o << "{\n  \"version\": 1,\n  \"entries\": [\n";
   bool firstEntry = true;
   for (auto &kv : table) {
-    int op = kv.first / 1000, rest = kv.first % 1000;
+    int es = kv.first / 100000, op = kv.first % 100000 / 1000, rest = kv.first % 1000;
     if (!firstEntry) o << ",\n";
     firstEntry = false;
-    o << "    {\"op\": " << op << ", \"bucket\": " << rest / 2 << ", \"registered\": " << rest % 2
+    o << "    {\"op\": " << op << ", \"elem_size\": " << es << ", \"bucket\": " << rest / 2 << ", \"registered\": " << rest % 2
       << ", \"algo\": " << kv.second.algo << ", \"nctas\": " << kv.second.nCtas << ", \"usec\": " << kv.second.usec
       << ", \"best_usec\": " << kv.second.bestUsec << "}";
   }
@@ -165,15 +173,16 @@ flagcxResult_t Tuner::fromJson(const std::string &text) {
       return p == std::string::npos ? dflt : atof(obj.c_str() + p + 1);
     };
     int op = (int)field("op", -1), bucket = (int)field("bucket", -1), reg = (int)field("registered", 0);
+    int es = (int)field("elem_size", 0); // absent in tables written before the key had it
     TuneChoice ch;
     ch.algo = (int)field("algo", -1);
     ch.nCtas = (int)field("nctas", 0);
     ch.usec = (float)field("usec", 0);
     ch.bestUsec = (float)field("best_usec", 0);
     if (op < 0 || op >= flagcxNumCommOps || bucket < 0 || bucket > 62 || ch.algo < 0 || ch.algo >= FLAGCX_ALGO_COUNT ||
-        ch.nCtas < 1 || ch.nCtas > FLAGCX_COLL_BARRIER_SLOTS)
+        ch.nCtas < 1 || ch.nCtas > FLAGCX_COLL_BARRIER_SLOTS || es < 0 || es > 8)
       return flagcxInvalidArgument;
-    parsed[keyOf((flagcxCommOp_t)op, bucket, reg != 0)] = ch;
+    parsed[keyOf((flagcxCommOp_t)op, bucket, reg != 0, es)] = ch;
     pos = end + 1;
   }
   table = parsed;
@@ -333,7 +342,7 @@ flagcxResult_t Tuner::tune(flagcxComm *c, flagcxCommOp_t op, flagcxDataType_t dt
       if (baseUs > 0 && bestUs >= 0.95f * baseUs) { ch = base; ch.usec = baseUs; } // hysteresis
       else { ch.algo = best.algo; ch.nCtas = best.nCtas; ch.usec = bestUs; }
       ch.bestUsec = bestUs;
-      table[keyOf(op, bucketOf(bytes), registered != 0)] = ch;
+      table[keyOf(op, bucketOf(bytes), registered != 0, elemClass(op, (int)getFlagcxDataTypeSize(dtype)))] = ch;
       if (c->rank == 0)
         FCX_INFO(SUB_TUNING, "%s %zu B %s: algo %d ctas %d %.1f us (heuristic %.1f us)", commOpName(op), bytes,
                  registered ? "registered" : "staged", ch.algo, ch.nCtas, ch.usec, baseUs);

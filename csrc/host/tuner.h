@@ -31,7 +31,10 @@ struct Tuner {
   flagcxResult_t init(flagcxComm *c);
   // registered: 1 when the buffers need no staging.  nvlsOk: multimem usable for
   // this call.  Always returns a concrete algorithm and CTA count.
-  TuneChoice choose(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk) const;
+  // elemSize: bytes per element for the reducing operations (a table may hold different
+  // winners for 2- and 4-byte types: the adds per byte differ), 0 for pure copies or "any".
+  // A lookup falls back to the size-agnostic entry, then to any entry of the bucket.
+  TuneChoice choose(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk, int elemSize = 0) const;
   TuneChoice heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool registered, bool nvlsOk) const;
   flagcxResult_t tune(flagcxComm *c, flagcxCommOp_t op, flagcxDataType_t dtype, size_t minBytes,
                       size_t maxBytes, int iters);
@@ -41,7 +44,7 @@ struct Tuner {
   flagcxResult_t fromJson(const std::string &text);
 
   static int bucketOf(size_t bytes); // ceil(log2(bytes))
-  // key = op * 1000 + bucket * 2 + registered
+  // key = elemSize * 100000 + op * 1000 + bucket * 2 + registered
   std::map<int, TuneChoice> table;
   int maxCtas = 32;
   int forcedAlgo = FLAGCX_ALGO_AUTO; // FLAGCX_ALGO

@@ -124,6 +124,20 @@ static void testTuner() {
   u.maxCtas = 48;
   EXPECT(u.fromJson(t.toJson()) == flagcxSuccess);
   EXPECT(u.table.size() == 1 && u.choose(flagcxCommOpAllReduce, 8 << 10, 8, true, false).nCtas == 7);
+  // an entry for 2-byte elements wins for bf16 calls of that bucket; 4-byte calls keep the
+  // size-agnostic entry; a table without elem_size (older files) still loads
+  TuneChoice two;
+  two.algo = FLAGCX_ALGO_TWOSHOT;
+  two.nCtas = 9;
+  t.table[2 * 100000 + (int)flagcxCommOpAllReduce * 1000 + 13 * 2 + 1] = two;
+  EXPECT(t.choose(flagcxCommOpAllReduce, 8 << 10, 8, true, false, 2).nCtas == 9);
+  EXPECT(t.choose(flagcxCommOpAllReduce, 8 << 10, 8, true, false, 4).nCtas == 7);
+  EXPECT(t.choose(flagcxCommOpAllGather, 8 << 10, 8, true, false, 2).algo != FLAGCX_ALGO_TWOSHOT);
+  EXPECT(u.fromJson(t.toJson()) == flagcxSuccess && u.table.size() == 2);
+  EXPECT(u.choose(flagcxCommOpAllReduce, 8 << 10, 8, true, false, 2).nCtas == 9);
+  t.table.erase(2 * 100000 + (int)flagcxCommOpAllReduce * 1000 + 13 * 2 + 1);
+  EXPECT(u.fromJson("{\"entries\": [{\"op\": 6, \"bucket\": 13, \"registered\": 1, \"algo\": 1, \"nctas\": 5}]}") == flagcxSuccess);
+  EXPECT(u.choose(flagcxCommOpAllReduce, 8 << 10, 8, true, false, 2).nCtas == 5);
   EXPECT(u.fromJson("{\"entries\": [{\"op\": 99, \"bucket\": 3}]}") == flagcxInvalidArgument);
   EXPECT(u.fromJson("not json") == flagcxInvalidArgument);
   // an NVLS entry is ignored when multimem is not usable for the call
