@@ -81,7 +81,7 @@ TuneChoice Tuner::heuristic(flagcxCommOp_t op, size_t bytes, int nranks, bool re
       // Callers that overlap their collectives with compute (a training framework's
       // gradient reduce-scatter) do better with the copy engines carrying the bytes and a
       // few CTAs adding from local memory: FLAGCX_COPY_ENGINE_MIN_BYTES > 0 asks for that
-      // from the given total size on.  The torch backend sets it (32 MiB) unless told otherwise.
+      // from the given total size on (off by default).
       static const int64_t ceMin = readParam("COPY_ENGINE_MIN_BYTES", 0);
       if (ceMin > 0 && bytes >= (size_t)ceMin && nranks > 1) {
         ch.algo = FLAGCX_ALGO_COPY_ENGINE;

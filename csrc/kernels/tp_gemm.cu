@@ -280,22 +280,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint4 *stg = s.epi[warp - 2];
     int acc = 0;
     uint32_t accPhase = 0;
-    // reduce-scatter: a tile sent to a peer is counted in on that peer one tile later, when
-    // its TMA stores have long completed, so the epilogue never sits out an NVLink round trip
-    int pendOwner = -1, pendRb = 0;
-    // Every epilogue warp counts its own quarter of the tile in (the owner waits for four
-    // arrivals per tile): no barrier between the warps, so a warp that gives up after a
-    // timed-out wait can never leave the others stuck.
-    auto countInPending = [&](bool fourNewerGroups) {
-      if (pendOwner < 0) return;
-      if (lane == 0) {
-        if (fourNewerGroups) bulkWaitDone<BN / kEpiCols>(); else bulkWaitDone<0>();
-        fenceProxyAsync();
-        fcxdev::fenceSys();
-        fcxdev::redAddReleaseSys(a.rowFlags[pendOwner] + kFlagStride * pendRb, 1ull);
-      }
-      pendOwner = -1;
-    };
     for (int tile = unit; tile < nTiles; tile += units) {
       int tm, tn;
       tileCoords(a, rank, tile, tilesN, TM, &tm, &tn);
@@ -323,13 +307,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           // them to the accumulator tile on its way out and store the final rows.
           dbase = a.out + rowLocal * a.N;
           if (n > 1) {
-            // Never wait while a count of mine is still undelivered: the peer that needs it
-            // may be waiting for it in this very place, and so on round the ranks.
-            countInPending(false);
             bool ok = true;
             if (lane == 0)
               ok = waitFlagGe(c, a.rowFlags[rank] + kFlagStride * (rowLocal / BM),
-                              a.epoch * (unsigned long long)((n - 1) * tilesN * 4), abortFlag, 0xffffffffu);
+                              a.epoch * (unsigned long long)((n - 1) * tilesN), abortFlag, 0xffffffffu);
             if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
             others = a.partial[rank] + rowLocal * a.N + (size_t)tn * BN;
           }
@@ -417,17 +398,23 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (PAIR && !leader) mbarArriveCluster(mapToCta(smemAddr(&s.tmemEmpty[acc]), 0));
         else mbarArrive(&s.tmemEmpty[acc]);
       }
-      if (a.mode == kGemmReduceScatter) {
-        // the previous remote tile: this tile put four newer store groups behind it, or none
-        countInPending(tmaOut);
-        if (owner != rank) {
-          pendOwner = owner;
-          pendRb = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
+      if (a.mode == kGemmReduceScatter && owner != rank) {
+        // Count the tile in on its owner once all four epilogue warps' stores are complete:
+        // ONE remote atomic per tile.  (Counting in one tile later, per warp, was tried: with
+        // more than two ranks the counts a rank still held while it waited for its own rows
+        // closed a circular wait, and once that was fixed the four atomics per tile on
+        // lines the owner's CTAs poll cost more than the deferral saved: 704 against
+        // 426-497 us at 8 ranks.)
+        if (lane == 0) { bulkWaitDone<0>(); fenceProxyAsync(); }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          fcxdev::fenceSys();
+          const int rbLocal = (int)(((size_t)tm * TM + ctaRank * BM - (size_t)owner * a.rowsPerRank) / BM);
+          fcxdev::redAddReleaseSys(a.rowFlags[owner] + kFlagStride * rbLocal, 1ull);
         }
       }
       if (++acc == 2) { acc = 0; accPhase ^= 1; }
     }
-    countInPending(false);
   } else if (warp >= 6 && a.mode == kAllGatherGemm && n > 1 && a.pushThreads) {
     // ---- pusher, thread flavour: warps 6 and 7 of EVERY CTA copy this CTA's share of each
     // 128-row chunk of my shard to all peers with plain 16-byte loads and posted stores

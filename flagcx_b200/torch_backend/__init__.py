@@ -55,9 +55,6 @@ class Options:
 
 
 def _create(dist_backend_opts, pg_options):
-    # torch runs its large reduce-scatters (FSDP gradients) beside compute kernels: have the
-    # copy engines carry them unless the user has decided otherwise
-    os.environ.setdefault("FLAGCX_COPY_ENGINE_MIN_BYTES", str(32 << 20))
     o = pg_options if isinstance(pg_options, Options) else Options(
         enable_tuner=os.environ.get("FLAGCX_TORCH_ENABLE_TUNER", "0") not in ("", "0"))
     return ext().create_backend(dist_backend_opts.store, dist_backend_opts.group_rank, dist_backend_opts.group_size,

@@ -1,11 +1,12 @@
-"""Host-side model of the count-in protocol of the fused GEMM -> reduce-scatter kernel
-(csrc/kernels/tp_gemm.cu): every CTA pair walks its tiles in the kernel's order (peers'
-rows first, own rows last), sends a partial tile to its owner and counts it in ONE TILE
-LATER, and may only finish an own tile once all peers have counted theirs in.  The model
-checks that the protocol always makes progress.  Delivering a pending count only after
-the next tile -- also when that next tile is an own tile that has to wait -- completes
-with 2 ranks and dead-locks with 4 and 8 (ranks wait on each other round the ring while
-holding each other's counts); delivering it before the wait never blocks."""
+"""Host-side model of count-in protocols for the fused GEMM -> reduce-scatter kernel
+(csrc/kernels/tp_gemm.cu).  Every CTA pair walks its tiles in the kernel's order (peers'
+rows first, own rows last), sends a partial tile to its owner and counts it in, and may
+only finish an own tile once all peers have counted theirs in.  The kernel counts a tile in
+at once.  A variant that counted in ONE TILE LATER (to hide the NVLink round trip) was
+tried on GPUs: it completed with 2 ranks and timed out with 8.  This model shows why --
+ranks wait on each other round the ring while holding each other's counts -- and that
+delivering the pending count before the wait restores progress; it guards any future
+attempt at deferral."""
 import pytest
 
 
