@@ -204,6 +204,26 @@ def rank_that_dies(rank, n, uid, victim):
     return 0
 
 
+def rank_that_is_late(rank, n, uid, late, delay_s):
+    """Failure on the host without a dead process: one rank reaches the collective only
+    after the others' deadline has passed.  The punctual ranks get an error code when their
+    deadline runs out; the late rank gets one too when it finally calls (its peers have given
+    up), and nobody hangs."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    x = np.ones(1 << 14, np.float32)
+    out = np.empty_like(x)
+    comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)  # connections are up now
+    if rank == late:
+        time.sleep(delay_s)
+    t0 = time.time()
+    try:
+        comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+        code = 0
+    except capi.FlagcxError as e:
+        code = e.code
+    return {"code": code, "seconds": time.time() - t0}
+
+
 def rank_that_never_joins(rank, n, uid):
     """Rank n-1 never calls flagcxCommInitRank: the others time out with an error."""
     if rank == n - 1:

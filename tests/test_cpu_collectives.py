@@ -86,6 +86,18 @@ def test_dead_rank_gives_an_error_not_a_hang(shm):
     assert all(code in (capi.flagcxRemoteError, capi.flagcxSystemError) for code in res.values()), res
 
 
+@pytest.mark.parametrize("shm", [0, 1])
+def test_late_rank_costs_a_deadline_not_a_hang(shm):
+    res = run_ranks(3, "rank_that_is_late", 2, 4.0, env={"FLAGCX_SOCKET_TIMEOUT_MS": 1500, "FLAGCX_HOST_SHM": shm},
+                    timeout=90)
+    for r in (0, 1):  # gave up when their deadline ran out, well before the late rank arrived
+        assert res[r]["code"] in (capi.flagcxRemoteError, capi.flagcxSystemError), res
+        assert res[r]["seconds"] < 3.9, res
+    # the late rank finds nobody waiting: an error (or, if its part needed no peer any more, success), never a hang
+    assert res[2]["code"] in (0, capi.flagcxRemoteError, capi.flagcxSystemError), res
+    assert res[2]["seconds"] < 10, res
+
+
 def test_absent_rank_times_out_at_init():
     res = run_ranks(2, "rank_that_never_joins", env={"FLAGCX_SOCKET_TIMEOUT_MS": 1500}, timeout=60)
     assert res[1] == "absent"
