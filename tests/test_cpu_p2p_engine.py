@@ -8,3 +8,15 @@ def test_one_sided_reads_writes_and_notifications_between_two_processes(tmp_path
     for rank, worst in res.items():
         bad = {k: v for k, v in worst.items() if v > 0.5}
         assert not bad, (rank, bad)
+
+
+def test_c_example_of_the_transfer_engine():
+    """csrc/examples/p2p_transfer.cc: the engine's C API from a program that forks its owner."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run(["make", "-C", os.path.join(root, "csrc"), "examples"], check=True, capture_output=True)
+    exe = os.path.join(root, "csrc", "build", "examples", "p2p_transfer")
+    res = subprocess.run([exe, str(5 * (1 << 20) + 17)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "0 wrong" in res.stdout and res.stdout.strip().endswith("ok"), res.stdout
