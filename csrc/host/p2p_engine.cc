@@ -13,6 +13,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <deque>
+#include <iterator>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -93,6 +94,7 @@ struct flagcxP2pEngine {
   std::map<uint64_t, Hello> halfHello;
   std::deque<flagcxP2pConn *> accepted;       // complete, not yet handed to flagcxP2pEngineAccept
   std::vector<flagcxP2pConn *> conns;         // everything alive, for teardown
+  std::map<std::string, flagcxP2pConn *> sessions; // flagcxP2pEngineGetConn's cache, by "ip:port"
 
   bool findRegion(uintptr_t a, size_t len, Region *out) {
     std::lock_guard<std::mutex> lk(mu);
@@ -477,6 +479,21 @@ flagcxResult_t flagcxP2pEngineConnect(flagcxP2pEngine_t e, const char *ipPort, f
   return flagcxSuccess;
 }
 
+flagcxResult_t flagcxP2pEngineGetConn(flagcxP2pEngine_t e, const char *ipPort, flagcxP2pConn_t *conn) {
+  if (!e || !ipPort || !conn) return flagcxInvalidArgument;
+  {
+    std::lock_guard<std::mutex> lk(e->mu);
+    auto it = e->sessions.find(ipPort);
+    if (it != e->sessions.end() && !it->second->stop.load()) { *conn = it->second; return flagcxSuccess; }
+  }
+  flagcxP2pConn_t fresh = nullptr;
+  FCXCHECK(flagcxP2pEngineConnect(e, ipPort, &fresh));
+  std::lock_guard<std::mutex> lk(e->mu);
+  e->sessions[ipPort] = fresh; // a broken predecessor stays in `conns` and is torn down with the engine
+  *conn = fresh;
+  return flagcxSuccess;
+}
+
 flagcxResult_t flagcxP2pEngineAccept(flagcxP2pEngine_t e, flagcxP2pConn_t *conn, int waitMs) {
   if (!e || !conn) return flagcxInvalidArgument;
   std::unique_lock<std::mutex> lk(e->mu);
@@ -496,6 +513,8 @@ flagcxResult_t flagcxP2pConnDestroy(flagcxP2pConn_t c) {
     std::lock_guard<std::mutex> lk(e->mu);
     e->conns.erase(std::remove(e->conns.begin(), e->conns.end(), c), e->conns.end());
     e->accepted.erase(std::remove(e->accepted.begin(), e->accepted.end(), c), e->accepted.end());
+    for (auto it = e->sessions.begin(); it != e->sessions.end();)
+      it = it->second == c ? e->sessions.erase(it) : std::next(it);
   }
   if (!c->stop.load()) {
     std::lock_guard<std::mutex> lk(c->outMu);

@@ -183,9 +183,7 @@ flagcxResult_t flagcxTpAllGatherGemm(flagcxTpGemm_t h, const void *B, void *D, f
     a.chunkFlags[p] = (unsigned long long *)h->wFlags->peer[p];
   }
   const int sms = smCount();
-  a.pushThreads = readParam("TP_PUSH_THREADS", 0) != 0 ? 1 : 0;
-  // arrivals that complete a 128-row chunk: its K/16 pieces of 4 KiB (engine), or one per CTA (threads)
-  a.piecesPerChunk = a.pushThreads ? (pair ? sms & ~1 : sms) : h->K / 16;
+  a.piecesPerChunk = h->K / 16; // a chunk is 128 rows of K bf16 = K/16 pieces of 4 KiB
   cudaError_t e = launchTpGemm(stream ? stream->base : nullptr, h->tmGather, *tb, nullptr, c->dev, a, sms, pair);
   if (e != cudaSuccess) { FCX_WARN("all-gather GEMM launch failed: %s", cudaGetErrorString(e)); return flagcxUnhandledDeviceError; }
   return flagcxSuccess;

@@ -58,6 +58,10 @@ flagcxResult_t flagcxP2pEngineConnect(flagcxP2pEngine_t engine, const char *ipPo
 /* The next connection a peer has opened to this engine; timeoutMs < 0 waits for ever,
  * flagcxInProgress when none arrived in time. */
 flagcxResult_t flagcxP2pEngineAccept(flagcxP2pEngine_t engine, flagcxP2pConn_t *conn, int timeoutMs);
+/* The engine's connection to the peer listening at "ip:port": opened on the first call,
+ * returned from a cache afterwards.  The engine closes it at flagcxP2pEngineDestroy; destroying it
+ * earlier also takes it out of the cache. */
+flagcxResult_t flagcxP2pEngineGetConn(flagcxP2pEngine_t engine, const char *ipPort, flagcxP2pConn_t *conn);
 flagcxResult_t flagcxP2pConnDestroy(flagcxP2pConn_t conn);
 /* 1 when the peer runs on this machine (device memory is reached directly). */
 flagcxResult_t flagcxP2pConnIsLocal(flagcxP2pConn_t conn, int *isLocal);

@@ -400,10 +400,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (a.mode == kGemmReduceScatter && owner != rank) {
         // Count the tile in on its owner once all four epilogue warps' stores are complete:
-        // ONE remote atomic per tile.  (Counting in one tile later, per warp, was tried: with
-        // more than two ranks the counts a rank still held while it waited for its own rows
-        // closed a circular wait, and once that was fixed the four atomics per tile on
-        // lines the owner's CTAs poll cost more than the deferral saved: 704 against
+        // ONE remote atomic per tile, at once.  (Counting in one tile later, per warp, was
+        // tried: with more than two ranks the counts a rank still held while it waited for
+        // its own rows closed a circular wait, and with that fixed the four atomics per tile
+        // on lines the owner's CTAs poll cost more than the deferral saved: 704 against
         // 426-497 us at 8 ranks.)
         if (lane == 0) { bulkWaitDone<0>(); fenceProxyAsync(); }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -414,50 +414,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (++acc == 2) { acc = 0; accPhase ^= 1; }
-    }
-  } else if (warp >= 6 && a.mode == kAllGatherGemm && n > 1 && a.pushThreads) {
-    // ---- pusher, thread flavour: warps 6 and 7 of EVERY CTA copy this CTA's share of each
-    // 128-row chunk of my shard to all peers with plain 16-byte loads and posted stores
-    // (eight loads in flight per thread), chunk 0 first, and count the chunk in on every
-    // peer once: one fence and one atomic per peer, chunk and CTA. ----
-    const int pt = threadIdx.x - 192; // 0..63
-    const int chunks = a.rowsPerRank / BM;
-    const size_t chunkVecs = (size_t)BM * a.K * 2 / 16;
-    const size_t shardVec0 = (size_t)rank * a.rowsPerRank * a.K * 2 / 16;
-    const size_t per = (chunkVecs + G - 1) / G;
-    const size_t vb = (size_t)blockIdx.x * per < chunkVecs ? (size_t)blockIdx.x * per : chunkVecs;
-    const size_t ve = vb + per < chunkVecs ? vb + per : chunkVecs;
-    const uint4 *src = (const uint4 *)a.gathered[rank] + shardVec0;
-    // (no wait in here and none on the abort flag: both warps run the same number of rounds)
-    for (int ch = 0; ch < chunks; ++ch) {
-      const size_t c0 = (size_t)ch * chunkVecs;
-      size_t i = vb + pt;
-      for (; i + 7 * 64 < ve; i += 8 * 64) {
-        uint4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = src[c0 + i + u * 64];
-        for (int k = 1; k < n; ++k) {
-          int p = rank + k; if (p >= n) p -= n;
-          uint4 *dst = (uint4 *)a.gathered[p] + shardVec0 + c0;
-#pragma unroll
-          for (int u = 0; u < 8; ++u) st16(dst + i + u * 64, v[u]);
-        }
-      }
-      for (; i < ve; i += 64) {
-        const uint4 v = src[c0 + i];
-        for (int k = 1; k < n; ++k) {
-          int p = rank + k; if (p >= n) p -= n;
-          st16((uint4 *)a.gathered[p] + shardVec0 + c0 + i, v);
-        }
-      }
-      asm volatile("bar.sync 2, 64;" ::: "memory"); // both pusher warps have issued their stores
-      if (pt == 0) {
-        fcxdev::fenceSys();
-        for (int k = 1; k < n; ++k) {
-          int p = rank + k; if (p >= n) p -= n;
-          redAddRelaxedSys(a.chunkFlags[p] + kFlagStride * ((size_t)rank * chunks + ch), 1ull);
-        }
-      }
     }
   } else if (warp == 6 && a.mode == kAllGatherGemm && n > 1) {
     // ---- pusher: one thread drives the copy engine.  My shard goes out in 4 KiB

@@ -22,8 +22,6 @@ struct TpGemmArgs {
   int rowsPerRank;  // M / nRanks
   int piecesPerChunk; // all-gather mode: a 128-row chunk travels in this many 4 KiB pieces per peer
   int groupRows;      // tile order: this many row blocks are walked together, column by column
-  int pushThreads;    // all-gather mode: 1 = two warps of every CTA push with plain loads/stores (a chunk
-                      // then counts gridDim.x arrivals per peer), 0 = one thread drives the bulk-copy engine
   unsigned long long epoch; // call counter of this handle, starts at 1
   // all-gather -> GEMM
   __nv_bfloat16 *gathered[FLAGCX_MAX_RANKS];      // rank p's gather buffer [M, K] as mapped here

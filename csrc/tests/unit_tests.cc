@@ -415,8 +415,9 @@ static void testP2pEngine() {
     if (r == flagcxRemoteError) ownerOk.fetch_add(1);
     flagcxP2pConnDestroy(c);
   });
-  flagcxP2pConn_t c = nullptr;
-  EXPECT(flagcxP2pEngineConnect(user, meta, &c) == flagcxSuccess);
+  flagcxP2pConn_t c = nullptr, again = nullptr;
+  EXPECT(flagcxP2pEngineGetConn(user, meta, &c) == flagcxSuccess);
+  EXPECT(flagcxP2pEngineGetConn(user, meta, &again) == flagcxSuccess && again == c); // cached
   if (c) {
     int local = 0;
     EXPECT(flagcxP2pConnIsLocal(c, &local) == flagcxSuccess && local == 1);

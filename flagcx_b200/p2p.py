@@ -138,6 +138,12 @@ class P2pEngine:
         capi.check(capi.lib().flagcxP2pEngineConnect(self.h, ip_port.encode(), C.byref(c)), "flagcxP2pEngineConnect")
         return P2pConn(c, self)
 
+    def get_conn(self, ip_port: str) -> P2pConn:
+        """The engine's cached connection to that peer (opened on first use; owned by the engine)."""
+        c = C.c_void_p()
+        capi.check(capi.lib().flagcxP2pEngineGetConn(self.h, ip_port.encode(), C.byref(c)), "flagcxP2pEngineGetConn")
+        return P2pConn(c, self)
+
     def accept(self, timeout_ms: int = -1) -> P2pConn | None:
         c = C.c_void_p()
         code = capi.lib().flagcxP2pEngineAccept(self.h, C.byref(c), timeout_ms)

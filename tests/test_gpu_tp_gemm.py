@@ -26,11 +26,8 @@ def test_tcgen05_gemm_matches_fp32_reference(M, N, K, pair, monkeypatch):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("push_threads", [0, 1])
-def test_fused_tensor_parallel_kernels_on_real_peers(push_threads):
-    """push_threads: who moves the all-gather's rows, the bulk-copy engine driven by one
-    thread per CTA (0) or two warps of every CTA with plain loads and stores (1)."""
+def test_fused_tensor_parallel_kernels_on_real_peers():
     n = 8 if torch.cuda.device_count() >= 8 else 4 if torch.cuda.device_count() >= 4 else 2
-    res = run_ranks(n, "tp_fused", 128 * n * 2, 512, 1024, env={"FLAGCX_TP_PUSH_THREADS": str(push_threads)}, timeout=300)
+    res = run_ranks(n, "tp_fused", 128 * n * 2, 512, 1024, timeout=300)
     for rank, errs in res.items():
         assert errs["ag_gemm"] < 2 ** -6 and errs["gemm_rs"] < 2 ** -5, (rank, errs)
