@@ -1089,3 +1089,46 @@ def p2p_engine_pair(rank, n, uid_unused, path, use_cuda):
     eng.close()
     return out
 
+
+def p2p_engine_owner_dies(rank, n, uid_unused, path):
+    """Failure on the host: the owner of the memory exits after the first transfer.  The
+    initiator's next calls come back with an error code within the socket deadline."""
+    import json
+    import os
+    import time
+    from flagcx_b200.p2p import P2pEngine
+    eng = P2pEngine(-1)
+    if rank == 0:
+        buf = np.zeros(1 << 16, np.uint8)
+        mr = eng.register(buf)
+        with open(path + ".tmp", "w") as f:
+            json.dump({"meta": eng.metadata, "desc": eng.describe(mr, buf).hex()}, f)
+        os.replace(path + ".tmp", path)
+        conn = eng.accept(60000)
+        assert conn.recv_notification(60000) == b"first done"
+        os._exit(0)  # no goodbye, no socket shutdown by the library
+    deadline = time.time() + 60
+    while not os.path.exists(path):
+        assert time.time() < deadline
+        time.sleep(0.05)
+    info = json.load(open(path))
+    conn = eng.connect(info["meta"])
+    src = np.ones(1 << 16, np.uint8)
+    conn.write(src, bytes.fromhex(info["desc"]))
+    conn.notify(b"first done")
+    time.sleep(0.5)
+    out = {}
+    t0 = time.time()
+    for name, fn in (("write", lambda: conn.write(src, bytes.fromhex(info["desc"]))),
+                     ("notify", lambda: conn.notify(b"anyone?")),
+                     ("read", lambda: conn.read(src, bytes.fromhex(info["desc"])))):
+        try:
+            fn()
+            out[name] = 0
+        except capi.FlagcxError as e:
+            out[name] = e.code
+    out["seconds"] = time.time() - t0
+    conn.close()
+    eng.close()
+    return out
+

@@ -10,6 +10,15 @@ def test_one_sided_reads_writes_and_notifications_between_two_processes(tmp_path
         assert not bad, (rank, bad)
 
 
+def test_owner_that_exits_turns_into_error_codes_not_a_hang(tmp_path):
+    from flagcx_b200 import capi
+    res = run_ranks(2, "p2p_engine_owner_dies", str(tmp_path / "owner.json"), env={"FLAGCX_SOCKET_TIMEOUT_MS": 2000},
+                    expect_dead=(0,), timeout=60)
+    r = res[1]
+    assert all(r[k] in (capi.flagcxRemoteError, capi.flagcxSystemError) for k in ("write", "notify", "read")), r
+    assert r["seconds"] < 8, r
+
+
 def test_c_example_of_the_transfer_engine():
     """csrc/examples/p2p_transfer.cc: the engine's C API from a program that forks its owner."""
     import os
