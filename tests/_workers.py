@@ -204,6 +204,45 @@ def rank_that_dies(rank, n, uid, victim):
     return 0
 
 
+def survivors_rebuild_a_smaller_communicator(rank, n, uid, victim, path):
+    """Elastic recovery on the host: a rank exits, the others see an error code, destroy the
+    communicator, agree on a new unique id (the lowest survivor creates it and publishes it
+    through a file) and carry on with n-1 ranks."""
+    comm = capi.Comm.init_rank(n, capi.unique_id_from_bytes(uid), rank)
+    x = np.full(1 << 12, float(rank + 1), np.float32)
+    out = np.empty_like(x)
+    comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+    assert out[0] == n * (n + 1) / 2
+    if rank == victim:
+        os._exit(0)
+    time.sleep(0.3)
+    try:
+        comm.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+        return {"error": 0}
+    except capi.FlagcxError as e:
+        code = e.code
+    try:
+        comm.abort()
+    except Exception:
+        pass
+    survivors = [r for r in range(n) if r != victim]
+    new_rank = survivors.index(rank)
+    if new_rank == 0:
+        with open(path + ".tmp", "wb") as f:
+            f.write(capi.unique_id_bytes(capi.get_unique_id()))
+        os.replace(path + ".tmp", path)
+    deadline = time.time() + 30
+    while not os.path.exists(path):
+        assert time.time() < deadline
+        time.sleep(0.05)
+    comm2 = capi.Comm.init_rank(len(survivors), capi.unique_id_from_bytes(open(path, "rb").read()), new_rank)
+    comm2.all_reduce(x, out, x.size, capi.FLOAT, capi.SUM)
+    want = float(sum(r + 1 for r in survivors))
+    ok = bool(np.all(out == want))
+    comm2.destroy()
+    return {"error": code, "recovered": ok, "new_world": len(survivors)}
+
+
 def rank_that_is_late(rank, n, uid, late, delay_s):
     """Failure on the host without a dead process: one rank reaches the collective only
     after the others' deadline has passed.  The punctual ranks get an error code when their

@@ -98,6 +98,14 @@ def test_late_rank_costs_a_deadline_not_a_hang(shm):
     assert res[2]["seconds"] < 10, res
 
 
+def test_survivors_destroy_and_rebuild_a_smaller_communicator(tmp_path):
+    res = run_ranks(3, "survivors_rebuild_a_smaller_communicator", 1, str(tmp_path / "new_id"),
+                    env={"FLAGCX_SOCKET_TIMEOUT_MS": 3000}, expect_dead=(1,), timeout=90)
+    assert set(res) == {0, 2}
+    for r in res.values():
+        assert r["error"] in (capi.flagcxRemoteError, capi.flagcxSystemError) and r["recovered"] and r["new_world"] == 2, res
+
+
 def test_absent_rank_times_out_at_init():
     res = run_ranks(2, "rank_that_never_joins", env={"FLAGCX_SOCKET_TIMEOUT_MS": 1500}, timeout=60)
     assert res[1] == "absent"
